@@ -39,7 +39,7 @@ class KVLayerView:
 
     def __init__(self, keys, values, table, window):
         self.keys = keys  # [blocks, kv_heads, 64, head_dim]
-        self.values = values
+        self.values = values  # None in a group with one plane
         self.table = table  # [slots, blocks_per_sequence] int32, -1 where nothing is held
         self.window = window
         self.block_tokens = BLOCK_TOKENS
@@ -64,7 +64,8 @@ class KVGroup:
         # one block and one table row more than the pool and the slots hand out: the spare slot (row max_slots) with
         # the spare block (n_blocks) at its first position, where a step's filler rows write and read
         self.storage = torch.zeros(
-            (len(self.layers), 2, n_blocks + 1, request.kvheads, BLOCK_TOKENS, request.head_dim), dtype=dtype, device=device
+            (len(self.layers), request.planes, n_blocks + 1, request.kvheads, BLOCK_TOKENS, request.head_dim), dtype=dtype,
+            device=device
         )
         self.table_host = torch.full((max_slots + 1, blocks_per_sequence), -1, dtype=torch.int32)
         self.table_host[max_slots, 0] = n_blocks
@@ -137,7 +138,8 @@ class KVGroup:
 
     def view(self, layer: int) -> KVLayerView:
         i = self.layers.index(layer)
-        return KVLayerView(self.storage[i, 0], self.storage[i, 1], self.table, self.request.window)
+        return KVLayerView(self.storage[i, 0], self.storage[i, 1] if self.request.planes > 1 else None, self.table,
+                           self.request.window)
 
 
 class StateGroup:
@@ -161,10 +163,13 @@ class Cache:
 
     ``layer_requests[i]`` is what layer i's mixer asks for (None: nothing).  ``max_tokens`` is the most
     tokens that live sequences hold at any time, each sequence's count rounded up to a multiple of 64.
+    ``named_requests``: what parts outside the layers ask for (the embedding's state of a sequence), by a name under
+    which ``layer_view(name)`` finds it.
     """
 
     def __init__(self, layer_requests: Sequence[Optional[Union[KVRequest, StateRequest]]], max_tokens: int,
-                 max_positions: int, dtype: torch.dtype, device, max_slots: Optional[int] = None) -> None:
+                 max_positions: int, dtype: torch.dtype, device, max_slots: Optional[int] = None,
+                 named_requests: Optional[Dict[str, Union[KVRequest, StateRequest]]] = None) -> None:
         self.device = torch.device(device)
         self.dtype = dtype
         self.max_positions = int(max_positions)
@@ -182,9 +187,9 @@ class Cache:
         self.length = [0] * self.max_slots
         self.position = [0] * self.max_slots
         self.groups: List[Union[KVGroup, StateGroup]] = []
-        self._group_of_layer: Dict[int, Union[KVGroup, StateGroup]] = {}
+        self._group_of_layer: Dict[Union[int, str], Union[KVGroup, StateGroup]] = {}
         by_request: Dict[object, List[int]] = {}
-        for layer, req in enumerate(layer_requests):
+        for layer, req in list(enumerate(layer_requests)) + list((named_requests or {}).items()):
             if req is not None:
                 by_request.setdefault(req, []).append(layer)
         for req, layers in by_request.items():
@@ -287,7 +292,7 @@ class Cache:
         """The position at which the sequence in ``slot`` started."""
         return self.position[slot] - self.length[slot]
 
-    def layer_view(self, layer: int):
+    def layer_view(self, layer: Union[int, str]):
         g = self._group_of_layer.get(layer)
         return None if g is None else g.view(layer)
 
@@ -301,5 +306,5 @@ class Cache:
         total = 0
         for g in self.groups:
             if isinstance(g, KVGroup):
-                total += 2 * len(g.layers) * g.request.kvheads * g.request.head_dim * g.storage.element_size()
+                total += g.request.planes * len(g.layers) * g.request.kvheads * g.request.head_dim * g.storage.element_size()
         return total

@@ -9,11 +9,13 @@ import torch
 
 @dataclasses.dataclass(frozen=True)
 class KVRequest:
-    """Keys and values of every cached position (``window == 0``) or of the last ``window`` positions."""
+    """Keys and values of every cached position (``window == 0``) or of the last ``window`` positions.
+    ``planes == 1``: one row per position and head instead of a key and a value (a latent from which both are made)."""
 
     kvheads: int
     head_dim: int
     window: int = 0
+    planes: int = 2
 
 
 @dataclasses.dataclass(frozen=True)

@@ -70,16 +70,23 @@ class FeedForwardSpec:
 class BlockSpec:
     """One layer: its norms, mixer and feed-forward and their arrangement, which names the block class in the
     registry (``fms_b200.parts.register_block``).  ``arrangement == "pre_norm"``:
-    x += mixer(norm1(x)); x += feed_forward(norm2(x)).  The names are those under which the layer's
-    parts appear in weight names (``ln``, ``attn``, ``ff_ln``, ``ff_sub_layer`` for Llama)."""
+    x += mixer(norm1(x)); x += feed_forward(norm2(x)).  ``arrangement == "sandwich"``: every sublayer's output is
+    normed once more before it is added, x += norm1b(mixer(norm1(x))); x += norm2b(feed_forward(norm2(x))); the two
+    further norms are ``mixer_post_norm`` and ``feed_forward_post_norm``, and a layer without a feed-forward
+    (``feed_forward is None``) ends after its mixer.  The names are those under which the layer's
+    parts appear in weight names (``ln``, ``attn``, ``ff_ln``, ``ff_sub_layer`` for Llama); ``post_names`` those of
+    the two further norms."""
 
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]
     mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward_norm: Optional[NormSpec]
     arrangement: str = "pre_norm"
     names: Tuple[str, str, str, str] = ("ln", "attn", "ff_ln", "ff_sub_layer")
     options: Tuple[Tuple[str, Any], ...] = ()  # what another arrangement needs (a residual multiplier, ...)
+    mixer_post_norm: Optional[NormSpec] = None
+    feed_forward_post_norm: Optional[NormSpec] = None
+    post_names: Tuple[str, str] = ("post_ln", "ff_post_ln")
 
 
 @dataclasses.dataclass(frozen=True)
@@ -97,6 +104,17 @@ class LayerCall:
 
 
 @dataclasses.dataclass(frozen=True)
+class EmbeddingSpec:
+    """How token ids become the first rows of the residual stream.  ``kind == "table"``: a row of the token table.
+    ``kind == "pair_hash"``: that row plus a row of a second table, found by hashing the token with the one before it:
+    row (previous * mul_prev + token * mul_cur) mod buckets, and row ``buckets`` (the table has buckets + 1 rows) for
+    a sequence's first token; options ``buckets``, ``mul_prev``, ``mul_cur``, ``name`` (the second table's tensor)."""
+
+    kind: str = "table"
+    options: Tuple[Tuple[str, Any], ...] = ()
+
+
+@dataclasses.dataclass(frozen=True)
 class DecoderSpec:
     vocab_size: int
     dim: int
@@ -109,6 +127,7 @@ class DecoderSpec:
     names: Tuple[str, str, str, str] = ("base_model.embedding", "base_model.layers", "base_model.dec_norm", "head")
     embedding_scale: float = 1.0  # the embedded rows are multiplied by it as they enter the residual stream
     logit_scale: float = 1.0  # the logits are multiplied by it
+    embedding: EmbeddingSpec = EmbeddingSpec()
 
     def __post_init__(self):
         n = len(self.layers)

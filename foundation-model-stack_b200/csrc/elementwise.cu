@@ -61,6 +61,64 @@ FMS_API int fms_embed_rows(const void* table, int table_dtype, const int* tokens
 }
 
 // ---------------------------------------------------------------------------------------------------
+// embedding with a hashed table of token pairs beside the token table:
+//   out[t, :] = scale * (float(table[tokens[t]]) + float(pairs[row(t)]))
+//   row(t) = (previous * mul_prev + tokens[t] * mul_cur) mod buckets, or `buckets` (the table's last row) for the token
+//   at place 0 of its sequence.  The previous token of a step's first row comes from the sequence's state
+//   (last_token[slot], one int per slot), which the block of that row then sets to the step's last token of the
+//   sequence: no other block touches it.  64-bit integer arithmetic.
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_pair_hash_kernel(const T* table, const T* pairs,
+                                       const int* tokens, const int* positions,
+                                       const int* token_seq, const int* first_row,
+                                       const int* slots, int* last_token,
+                                       float* out, int dim, int vocab, long long buckets,
+                                       long long mul_prev, long long mul_cur, float scale, int update_state,
+                                       int n_seqs, int n_slots, int* error_flag) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int tok = tokens[t];
+  const int seq = token_seq[t];
+  if (!FMS_IN(seq, n_seqs)) return;
+  const int slot = slots[seq], first = first_row[seq];
+  if (!FMS_IN(slot, n_slots)) return;
+  const bool ok = tok >= 0 && tok < vocab;
+  if (!ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
+  long long row = buckets;
+  if (__ldcg(positions + t) != 0) {  // written by the kernel right before this one in a decode step
+    const long long prev = t == first ? last_token[slot] : tokens[t - 1];
+    row = (prev * mul_prev + (long long)tok * mul_cur) % buckets;
+    if (row < 0) row += buckets;
+  }
+  if (t == first && update_state) {
+    __syncthreads();  // every thread of this block has read the state
+    if (threadIdx.x == 0) last_token[slot] = tokens[first_row[seq + 1] - 1];
+  }
+  const T* src = table + (size_t)(ok ? tok : 0) * dim;
+  const T* two = pairs + (size_t)(ok ? row : buckets) * dim;
+  float* dst = out + (size_t)t * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = ok ? scale * (to_f32(src[d]) + to_f32(two[d])) : 0.f;
+}
+
+FMS_API int fms_embed_pair_hash(const void* table, const void* pairs, int table_dtype, const int* tokens,
+                                const int* positions, const int* token_seq, const int* first_row, const int* slots,
+                                int* last_token, float* out, int n_tokens, int dim, int vocab, long buckets, long mul_prev,
+                                long mul_cur, float scale, int update_state, int n_seqs, int n_slots, int* error_flag,
+                                cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (dim <= 0 || vocab <= 0 || buckets <= 0) return fms_fail("embed_pair_hash: dim %d, vocab %d, buckets %ld", dim, vocab, buckets);
+  const int threads = dim >= 1024 ? 256 : 128;
+  FMS_DISPATCH_DTYPE(table_dtype, T,
+                     fms_launch(embed_pair_hash_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, (const T*)table,
+                                (const T*)pairs, tokens, positions, token_seq, first_row, slots, last_token, out, dim,
+                                vocab, (long long)buckets, (long long)mul_prev, (long long)mul_cur, scale, update_state,
+                                n_seqs, n_slots, error_flag));
+  return fms_launch_status("embed_pair_hash");
+}
+
+// ---------------------------------------------------------------------------------------------------
 // residual add + RMSNorm                                     (reference: fms/modules/layernorm.py:56-69)
 //   x = residual[src] + delta[src]       float32; written back to residual unless rows are gathered
 //   out[r] = gain * x * rsqrt(mean(x^2) + eps)
@@ -211,6 +269,73 @@ FMS_API int fms_add_rmsnorm(float* residual, const void* delta, const void* gain
                      fms_launch(add_rmsnorm_kernel<T, TG>, dim3(n_rows), dim3(threads), 0, stream, residual,
                                 (const T*)delta, (const TG*)gain, eps, (T*)out, rows, dim, residual_rows)));
   return fms_launch_status("add_rmsnorm");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// a sublayer's output normed on its way into the residual stream, and the next norm, in one pass over the row:
+//   d = delta * (1 / sqrt(mean(delta^2) + post_eps)) * post_gain        (skipped where has_post == 0: d = delta)
+//   x = residual[src] + d                 float32; written back to residual unless rows are gathered
+//   out[r] = x * (1 / sqrt(mean(x^2) + eps)) * gain
+// Each gain is one number for the whole row (the vector pointer null) or a vector of `dim`.  One block per row.
+// ---------------------------------------------------------------------------------------------------
+template <typename T, typename TG>
+__global__ void normed_add_rmsnorm_kernel(float* residual, const T* delta, int has_post,
+                                          const TG* post_gain_vec, float post_gain, float post_eps,
+                                          const TG* gain_vec, float gain, float eps, T* out,
+                                          const int* rows, int dim, int residual_rows) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  if (!FMS_IN(src, residual_rows)) return;  // the whole block alike
+  float* res = residual + (size_t)src * dim;
+  const T* del = delta ? delta + (size_t)src * dim : nullptr;
+  float inv_d = 1.f;
+  if (del && has_post) {
+    float sd = 0.f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      const float v = to_f32(del[d]);
+      sd += v * v;
+    }
+    inv_d = 1.f / sqrtf(block_sum(sd, scratch) / (float)dim + post_eps);
+  }
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    float x = res[d];
+    if (del) {
+      float v = to_f32(del[d]);
+      if (has_post) v = v * inv_d * (post_gain_vec ? to_f32(post_gain_vec[d]) : post_gain);
+      x += v;
+      if (rows == nullptr) res[d] = x;
+    }
+    ss += x * x;
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+  T* o = out + (size_t)r * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    float x = res[d];  // this thread's own earlier store, where the sum was written back
+    if (rows != nullptr && del) {
+      float v = to_f32(del[d]);
+      if (has_post) v = v * inv_d * (post_gain_vec ? to_f32(post_gain_vec[d]) : post_gain);
+      x += v;
+    }
+    o[d] = from_f32<T>(x * inv * (gain_vec ? to_f32(gain_vec[d]) : gain));
+  }
+}
+
+FMS_API int fms_normed_add_rmsnorm(float* residual, const void* delta, int has_post, const void* post_gain_vec,
+                                   float post_gain, float post_eps, const void* gain_vec, float gain, float eps,
+                                   int gain_dtype, void* out, int dtype, const int* rows, int n_rows, int dim,
+                                   int residual_rows, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dim <= 0) return fms_fail("normed_add_rmsnorm: dim %d", dim);
+  const int threads = dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128));
+  FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG,
+                     fms_launch(normed_add_rmsnorm_kernel<T, TG>, dim3(n_rows), dim3(threads), 0, stream, residual,
+                                (const T*)delta, has_post, (const TG*)post_gain_vec, post_gain, post_eps,
+                                (const TG*)gain_vec, gain, eps, (T*)out, rows, dim, residual_rows)));
+  return fms_launch_status("normed_add_rmsnorm");
 }
 
 // ---------------------------------------------------------------------------------------------------

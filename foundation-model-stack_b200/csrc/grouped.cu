@@ -1,0 +1,358 @@
+// Products by groups of rows, and the routing of tokens to experts that makes such groups.
+//
+// grouped product: y[r, :] = x[r, :] . w[g]^T for the rows r of group g, w [groups, N, K].  The groups are either
+//   ragged  — rows offsets[g] .. offsets[g + 1] - 1 of x and y (tokens sorted by expert; the offsets live on the device,
+//             so a step needs no answer from the device before it launches), or
+//   uniform — the same `rows` rows for every group, group g reading x at column g * x_group_offset and writing y at
+//             column g * y_group_offset (the heads of one token matrix, each with a matrix of its own).
+// With glu != 0, w[g] holds 2 N rows, [gate; up], and y = act(gate) * (up + 1) with gate cut off above `limit`, up
+// clamped to +-limit and act(v) = v * sigmoid(alpha v): the gated unit of the routed experts.
+// Sums are float32, each output element one chain over k in order, whatever else is in the launch.
+//
+// routing: scores = sigmoid(x . router^T) in float32; the `top` largest (the lower index among equals) are a token's
+// experts and their scores its weights.  A (token, choice) pair becomes a row of the expert-sorted matrix:
+// xs[row] = weight * x[token], rounded to the compute dtype.  After the experts, out[token] = the sum of its
+// pairs' rows in the order of its choices, float32.
+#include "common.cuh"
+
+
+// Kernels of a step may start while the kernel before them is still running (programmatic dependent launch) and
+// read what that kernel wrote right after griddepcontrol.wait.  No pointer here is declared __restrict__: the
+// compiler must not turn such a read into a non-coherent load or move it ahead of the wait, and the few words of
+// bookkeeping that the kernel before wrote (positions, offsets, groups) are read with ld_fresh (from L2).
+#define __restrict__
+__device__ __forceinline__ int ld_fresh(const int* p) { return __ldcg(p); }
+__device__ __forceinline__ float ld_fresh(const float* p) { return __ldcg(p); }
+
+namespace {
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+__device__ __forceinline__ float glu_clamped(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * (1.f / (1.f + expf(-alpha * g))) * (u + 1.f);
+}
+
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(256) grouped_gemm_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                           T* __restrict__ y, const int* __restrict__ offsets,
+                                                           const int* __restrict__ tile_first, int groups, int rows,
+                                                           int N, int K, long x_row_stride, long x_group_offset,
+                                                           long y_row_stride, long y_group_offset, float limit,
+                                                           float alpha) {
+  __shared__ float xs[BK][BM + 4];
+  __shared__ float ws[GLU ? 2 : 1][BK][BN + 4];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  int g, m0, m_end;
+  if (offsets != nullptr) {
+    const int tile = blockIdx.y;
+    if (tile >= ld_fresh(tile_first + groups)) return;
+    g = 0;
+    while (g + 1 < groups && tile >= ld_fresh(tile_first + g + 1)) ++g;
+    m0 = ld_fresh(offsets + g) + (tile - ld_fresh(tile_first + g)) * BM;
+    m_end = ld_fresh(offsets + g + 1);
+  } else {
+    g = blockIdx.z;
+    m0 = blockIdx.y * BM;
+    m_end = rows;
+    x += (size_t)g * x_group_offset;
+    y += (size_t)g * y_group_offset;
+  }
+  const int n0 = blockIdx.x * BN;
+  const T* wg = w + (size_t)g * (GLU ? 2 : 1) * N * K;
+  const int tm = (tid / 16) * TM, tn = (tid % 16) * TN;
+  float acc[GLU ? 2 : 1][TM][TN];
+#pragma unroll
+  for (int h = 0; h < (GLU ? 2 : 1); ++h)
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[h][i][j] = 0.f;
+  const int lr = tid / 4, lk = (tid % 4) * 4;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    float xv[4] = {0.f, 0.f, 0.f, 0.f}, wv[GLU ? 2 : 1][4];
+    const int gm = m0 + lr, gn = n0 + lr, gk = k0 + lk;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (gm < m_end && gk + i < K) xv[i] = to_f32(x[(size_t)gm * x_row_stride + gk + i]);
+#pragma unroll
+    for (int h = 0; h < (GLU ? 2 : 1); ++h)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        wv[h][i] = (gn < N && gk + i < K) ? to_f32(wg[((size_t)h * N + gn) * K + gk + i]) : 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      xs[lk + i][lr] = xv[i];
+#pragma unroll
+      for (int h = 0; h < (GLU ? 2 : 1); ++h) ws[h][lk + i][lr] = wv[h][i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float a[TM];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = xs[k][tm + i];
+#pragma unroll
+      for (int h = 0; h < (GLU ? 2 : 1); ++h) {
+        float b[TN];
+#pragma unroll
+        for (int j = 0; j < TN; ++j) b[j] = ws[h][k][tn + j];
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+          for (int j = 0; j < TN; ++j) acc[h][i][j] = fmaf(a[i], b[j], acc[h][i][j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int gm = m0 + tm + i;
+    if (gm >= m_end) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int gn = n0 + tn + j;
+      if (gn >= N) continue;
+      const float v = GLU ? glu_clamped(acc[0][i][j], acc[GLU ? 1 : 0][i][j], limit, alpha) : acc[0][i][j];
+      y[(size_t)gm * y_row_stride + gn] = from_f32<T>(v);
+    }
+  }
+}
+
+// Few rows a group (a decode step's pairs): a block per (row, 8 outputs); every warp one output (two with glu), its
+// lanes striding over k.  The group of a row comes from `group_of_row`.  The sums are taken in another order than
+// the tiles' above, so the two differ by rounding.
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(256) grouped_gemv_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                           T* __restrict__ y, const int* __restrict__ group_of_row,
+                                                           int groups, int N, int K, float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const int g = ld_fresh(group_of_row + r);
+  if (g < 0 || !FMS_IN(g, groups)) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const T* xr = x + (size_t)r * K;
+  const T* w0 = w + ((size_t)g * (GLU ? 2 : 1) * N + n) * K;
+  const T* w1 = w0 + (size_t)N * K;
+  float a0 = 0.f, a1 = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    const float xv = to_f32(xr[k]);
+    a0 = fmaf(xv, to_f32(w0[k]), a0);
+    if (GLU) a1 = fmaf(xv, to_f32(w1[k]), a1);
+  }
+  a0 = warp_sum(a0);
+  if (GLU) a1 = warp_sum(a1);
+  if (lane == 0) y[(size_t)r * N + n] = from_f32<T>(GLU ? glu_clamped(a0, a1, limit, alpha) : a0);
+}
+
+// ---- routing -----------------------------------------------------------------------------------------
+// One block per token.  logits in shared memory; warp 0 then takes the `top` largest one after the other.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) route_kernel(const T* __restrict__ x, const TW* __restrict__ router,
+                                                    int* __restrict__ expert, float* __restrict__ weight,
+                                                    int dim, int experts, int top) {
+  extern __shared__ float sm[];  // dim values of x, then `experts` logits
+  float* xs = sm;
+  float* logit = sm + dim;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) xs[d] = to_f32(x[(size_t)t * dim + d]);
+  __syncthreads();
+  for (int e = warp; e < experts; e += 4) {
+    const TW* wr = router + (size_t)e * dim;
+    float a = 0.f;
+    for (int d = lane; d < dim; d += 32) a = fmaf(xs[d], to_f32(wr[d]), a);
+    a = warp_sum(a);
+    if (lane == 0) logit[e] = a;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = logit[e];
+      if (v > best || (v == best && e < at)) {
+        best = v;
+        at = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) {
+        best = ob;
+        at = oa;
+      }
+    }
+    if (at >= experts) at = k;  // every logit was NaN or -inf: any expert, so that nothing below reads outside
+    if (lane == 0) {
+      expert[(size_t)t * top + k] = at;
+      weight[(size_t)t * top + k] = 1.f / (1.f + expf(-best));
+      logit[at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+// One block: counts every expert's pairs (in shared memory), then offsets [experts + 1], tile_first [experts + 1]
+// (tiles of BM rows), and placed [experts] = 0: how many rows of each expert the next kernel has placed.
+__global__ void __launch_bounds__(256) route_offsets_kernel(const int* __restrict__ expert, int n_pairs,
+                                                            int* __restrict__ placed, int* __restrict__ offsets,
+                                                            int* __restrict__ tile_first, int experts) {
+  extern __shared__ int count[];
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = ld_fresh(expert + p);
+    if (FMS_IN(e, experts)) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  int row = 0, tile = 0;
+  for (int e = 0; e < experts; ++e) {
+    const int c = count[e];
+    offsets[e] = row;
+    tile_first[e] = tile;
+    row += c;
+    tile += (c + BM - 1) / BM;
+    placed[e] = 0;
+  }
+  offsets[experts] = row;
+  tile_first[experts] = tile;
+}
+
+// One block per pair: takes the next free row of its expert and writes the weighted token there.
+template <typename T>
+__global__ void __launch_bounds__(128) route_scatter_kernel(const T* __restrict__ x, const int* __restrict__ expert,
+                                                            const float* __restrict__ weight,
+                                                            const int* __restrict__ offsets, int* __restrict__ placed,
+                                                            int* __restrict__ row_of_pair, int* __restrict__ group_of_row,
+                                                            T* __restrict__ xs, int dim, int top, int experts, int n_pairs) {
+  __shared__ int where;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int p = blockIdx.x;
+  const int e = ld_fresh(expert + p);
+  if (!FMS_IN(e, experts)) return;
+  if (threadIdx.x == 0) {
+    where = ld_fresh(offsets + e) + atomicAdd(&placed[e], 1);
+    row_of_pair[p] = where;
+    if (FMS_IN(where, n_pairs)) group_of_row[where] = e;
+  }
+  __syncthreads();
+  const int row = where;
+  if (!FMS_IN(row, n_pairs)) return;
+  const float wgt = ld_fresh(weight + p);
+  const T* src = x + (size_t)(p / top) * dim;
+  T* dst = xs + (size_t)row * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = from_f32<T>(wgt * to_f32(src[d]));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) route_gather_kernel(const T* __restrict__ ys, const int* __restrict__ row_of_pair,
+                                                           T* __restrict__ out, int dim, int top, int n_pairs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int row = ld_fresh(row_of_pair + (size_t)t * top + k);
+      if (FMS_IN(row, n_pairs)) a += to_f32(ys[(size_t)row * dim + d]);
+    }
+    out[(size_t)t * dim + d] = from_f32<T>(a);
+  }
+}
+}  // namespace
+
+FMS_API int fms_grouped_tile_rows() { return BM; }
+
+// offsets null: uniform groups of `rows` rows; else ragged groups, `rows` = all rows of x, and tile_first as
+// fms_route leaves it.  few_rows != 0 (ragged, contiguous rows of K and N values): the row-by-row kernel, which reads
+// each row's group from group_of_row.
+FMS_API int fms_grouped_linear(const void* x, const void* w, void* y, int dtype, const int* offsets, const int* tile_first,
+                               const int* group_of_row, int groups, int rows, int N, int K, long x_row_stride,
+                               long x_group_offset, long y_row_stride, long y_group_offset, int glu, float limit,
+                               float alpha, int few_rows, cudaStream_t stream) {
+  if (rows <= 0 || groups <= 0 || N <= 0) return 0;
+  if (K <= 0) return fms_fail("grouped_linear: K %d", K);
+  if (few_rows) {
+    if (group_of_row == nullptr || x_row_stride != K || y_row_stride != N)
+      return fms_fail("grouped_linear: the row-by-row kernel takes contiguous rows and a group for each");
+    if (rows > 65535) return fms_fail("grouped_linear: %d rows are more than the row-by-row kernel takes", rows);
+    dim3 grid((N + 7) / 8, rows);
+    FMS_DISPATCH_DTYPE(dtype, T, {
+      if (glu)
+        fms_launch(grouped_gemv_kernel<T, true>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y, group_of_row,
+                   groups, N, K, limit, alpha);
+      else
+        fms_launch(grouped_gemv_kernel<T, false>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y,
+                   group_of_row, groups, N, K, limit, alpha);
+    });
+    return fms_launch_status("grouped_linear (few rows)");
+  }
+  dim3 grid((N + BN - 1) / BN, 1, 1);
+  if (offsets != nullptr) {
+    if (tile_first == nullptr) return fms_fail("grouped_linear: ragged groups need tile_first");
+    grid.y = (rows + BM - 1) / BM + groups;
+  } else {
+    grid.y = (rows + BM - 1) / BM;
+    grid.z = groups;
+  }
+  if (grid.y > 65535 || grid.z > 65535) return fms_fail("grouped_linear: %d rows, %d groups are more than one launch takes", rows, groups);
+  FMS_DISPATCH_DTYPE(dtype, T, {
+    if (glu)
+      fms_launch(grouped_gemm_kernel<T, true>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y, offsets,
+                 tile_first, groups, rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha);
+    else
+      fms_launch(grouped_gemm_kernel<T, false>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y, offsets,
+                 tile_first, groups, rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha);
+  });
+  return fms_launch_status("grouped_linear");
+}
+
+// x [n_tokens, dim] in `dtype`, router [experts, dim] in `router_dtype`.  Out: expert, weight [n_tokens, top];
+// offsets, tile_first [experts + 1]; row_of_pair [n_tokens * top]; group_of_row [n_tokens * top]; xs [n_tokens * top, dim].
+// counts [experts] is scratch: the rows of each expert that are placed so far.
+FMS_API int fms_route(const void* x, int dtype, const void* router, int router_dtype, int* expert, float* weight, int* counts,
+                      int* offsets, int* tile_first, int* row_of_pair, int* group_of_row, void* xs, int n_tokens, int dim,
+                      int experts, int top, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (dim <= 0 || experts <= 0 || top <= 0 || top > experts) return fms_fail("route: dim %d, experts %d, top %d", dim, experts, top);
+  const size_t smem = ((size_t)dim + experts) * sizeof(float);
+  if (smem > 200 * 1024) return fms_fail("route: rows of %d values and %d experts do not fit shared memory", dim, experts);
+  FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(router_dtype, TW, {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(route_kernel<T, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    fms_launch(route_kernel<T, TW>, dim3(n_tokens), dim3(128), smem, stream, (const T*)x, (const TW*)router, expert, weight,
+               dim, experts, top);
+  }));
+  if (fms_launch_status("route")) return 1;
+  const int n_pairs = n_tokens * top;
+  fms_launch(route_offsets_kernel, dim3(1), dim3(256), sizeof(int) * experts, stream, (const int*)expert, n_pairs, counts,
+             offsets, tile_first, experts);
+  if (fms_launch_status("route (offsets)")) return 1;
+  FMS_DISPATCH_DTYPE(dtype, T,
+                     fms_launch(route_scatter_kernel<T>, dim3(n_pairs), dim3(128), 0, stream, (const T*)x, (const int*)expert,
+                                (const float*)weight, (const int*)offsets, counts, row_of_pair, group_of_row, (T*)xs, dim,
+                                top, experts, n_pairs));
+  return fms_launch_status("route (scatter)");
+}
+
+FMS_API int fms_route_gather(const void* ys, int dtype, const int* row_of_pair, void* out, int n_tokens, int dim, int top,
+                             cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  FMS_DISPATCH_DTYPE(dtype, T,
+                     fms_launch(route_gather_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, (const T*)ys, row_of_pair,
+                                (T*)out, dim, top, n_tokens * top));
+  return fms_launch_status("route_gather");
+}

@@ -83,6 +83,22 @@ class Batch:
         b.len_before_host = list(len_before)
         return b
 
+    def row_chunks(self, chunk: int):
+        """(chunk_rows [chunks, 2] int32: first row and end of every run of up to ``chunk`` rows of one sequence;
+        first_chunk [n_seqs + 1] int32: where each sequence's runs start in that list), for kernels that walk a
+        sequence's rows run by run."""
+        key = ("chunks", chunk)
+        if key not in self._tiles:
+            rows, first, base = [], [0], 0
+            for n in self.num_new:
+                for r in range(0, n, chunk):
+                    rows.append((base + r, base + min(n, r + chunk)))
+                first.append(len(rows))
+                base += n
+            packed = torch.tensor([v for p in rows for v in p] + first, dtype=torch.int32).to(self.tokens.device)
+            self._tiles[key] = (packed[: 2 * len(rows)].view(-1, 2), packed[2 * len(rows):])
+        return self._tiles[key]
+
     def query_tiles(self, tile_rows: int) -> torch.Tensor:
         """[tiles, 2] int32: (sequence index, first row of the tile within the sequence's new tokens), for
         kernels that give each thread block ``tile_rows`` rows of one sequence."""

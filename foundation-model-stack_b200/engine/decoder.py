@@ -12,7 +12,8 @@ from ..config.specs import DecoderSpec
 from ..kernels import ops
 from ..parts.base import Part
 from ..parts import block as _blocks  # noqa: F401  (registers the built-in arrangement)
-from ..parts.registry import build_block, build_norm
+from ..parts import embedding as _embeddings  # noqa: F401  (registers the built-in embeddings)
+from ..parts.registry import build_block, build_embedding, build_norm
 
 
 def _add_path(root: Part, path: str, part: Part) -> Part:
@@ -31,8 +32,7 @@ class Decoder(Part):
         self.spec = spec
         self.dtype = dtype
         emb_name, layers_name, norm_name, head_name = spec.names
-        self.embedding = _add_path(self, emb_name, Part())
-        self.embedding.declare("weight", (spec.vocab_size, spec.dim), role="matrix")
+        self.embedding = _add_path(self, emb_name, build_embedding(spec.embedding, spec.vocab_size, spec.dim))
         layer_list = _add_path(self, layers_name, Part())
         self.blocks = [layer_list.add(str(i), build_block(b)) for i, b in enumerate(spec.layers)]
         self.final_norm = _add_path(self, norm_name, build_norm(spec.final_norm))
@@ -44,6 +44,11 @@ class Decoder(Part):
     def cache_requests(self):
         """Per layer, what its mixer asks of the cache."""
         return [b.cache_request() for b in self.blocks]
+
+    def named_cache_requests(self):
+        """What parts outside the layers ask of the cache, by the name under which the cache hands it back."""
+        request = self.embedding.cache_request()
+        return {} if request is None else {"embedding": request}
 
     def finalize(self, device, dtype=None) -> None:
         self.device = torch.device(device)
@@ -60,7 +65,7 @@ class Decoder(Part):
     def forward(self, batch, cache):
         if getattr(batch, "scratch", None) is not None:
             batch.scratch.clear()  # nothing of an earlier step with the same arrays (a decode step) is kept
-        residual = ops.embed(self.embedding.tensor("weight"), batch.tokens, self.spec.embedding_scale)
+        residual = self.embedding.forward(batch, cache.layer_view("embedding"), self.spec.embedding_scale)
         pending = None
         for call in self.spec.schedule:
             view = cache.layer_view(call.cache_layer)

@@ -93,7 +93,8 @@ class Engine:
         if self.device.type == "cuda":
             self._compile_what_this_model_needs(sampling)
         self.cache = Cache(self.decoder.cache_requests(), max_tokens, self.decoder.spec.max_positions,
-                           self.decoder.dtype, self.device, max_slots)
+                           self.decoder.dtype, self.device, max_slots,
+                           named_requests=self.decoder.named_cache_requests())
         self.use_graphs = use_graphs and self.device.type == "cuda"
         # decode steps of more than 8 sequences are filled up to one of a few sizes (``decode_rows``): it pays where a
         # size means a captured graph

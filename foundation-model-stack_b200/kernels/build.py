@@ -39,6 +39,9 @@ PLAIN_LIBRARIES = {
     "gemm_bf16_mid": ("gemm_bf16_mid.cu", []),
     "gemm_bf16_tc": ("gemm_bf16_tc.cu", []),
     "sampling": ("sampling.cu", []),
+    "recurrent": ("recurrent.cu", []),
+    "grouped": ("grouped.cu", []),
+    "latent_attention": ("latent_attention.cu", []),
 }
 
 _TAG = "_checked" if DEBUG_BOUNDS else ""

@@ -52,6 +52,16 @@ _SIGNATURES = {
     "fms_glu_bf16_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "fms_qkv_rope_store_bf16_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
                                    _I, _I, _I, _P],
+    "fms_embed_pair_hash": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _F, _I, _I, _I, _P, _P],
+    "fms_normed_add_rmsnorm": [_P, _P, _I, _P, _F, _F, _P, _F, _F, _I, _P, _I, _P, _I, _I, _I, _P],
+    "fms_mingru_scan": [_P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P],
+    "fms_grouped_linear": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _I, _F, _F, _I, _P],
+    "fms_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fms_route_gather": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "fms_latent_prepare": [_P, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
+                           _I, _I, _P, _P],
+    "fms_latent_attention": [_P, _P, _I, _P, _P, _L, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I,
+                             _I, _I, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
     "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P],
@@ -176,7 +186,48 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, scale: float = 1.0) -> torc
     return out
 
 
+def embed_pair_hash(table: torch.Tensor, pairs: torch.Tensor, batch, last_token: torch.Tensor, buckets: int,
+                    mul_prev: int, mul_cur: int, scale: float = 1.0) -> torch.Tensor:
+    """Float32 rows table[token] + pairs[(previous * mul_prev + token * mul_cur) mod buckets] (pairs[buckets] for the
+    token at place 0 of its sequence), times ``scale``.  ``last_token`` [slots, 1] int32 is each sequence's last
+    token so far: read for a step's first row, then set to the step's last token."""
+    n, dim = batch.tokens.shape[0], table.shape[1]
+    if pairs.dtype != table.dtype or pairs.shape != (buckets + 1, dim) or last_token.dtype != torch.int32:
+        raise KernelError("embed_pair_hash: the pair table has the token table's dtype and buckets + 1 rows of its width; "
+                          "the state is int32")
+    out = torch.empty((n, dim), dtype=torch.float32, device=table.device)
+    _call("elementwise", "fms_embed_pair_hash", _ptr(table), _ptr(pairs), _code(table.dtype), _ptr(batch.tokens),
+          _ptr(batch.positions), _ptr(batch.token_seq), _ptr(batch.first_row), _ptr(batch.slots), _ptr(last_token),
+          _ptr(out), n, dim, table.shape[0], int(buckets), int(mul_prev), int(mul_cur), float(scale), 1,
+          batch.slots.shape[0], last_token.shape[0], _ptr(error_flag(table.device)), _stream())
+    return out
+
+
 # ---- norm --------------------------------------------------------------------------------------------
+def normed_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], post, gain, out_dtype: torch.dtype,
+                       rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual (float32, in place) += post_norm(delta); returns norm(residual) in ``out_dtype``.  ``post`` and ``gain``
+    are (vector or None, number, eps): an RMS norm's gain as a vector of the row's width or as one number.  ``post``
+    None adds delta as it is.  With ``rows`` only those rows are computed and the residual is not written."""
+    dim = residual.shape[1]
+    n = rows.shape[0] if rows is not None else residual.shape[0]
+    if residual.dtype != torch.float32:
+        raise KernelError("the residual stream is float32")
+    if delta is not None and delta.dtype != out_dtype:
+        raise KernelError(f"sublayer output is {delta.dtype}, compute dtype is {out_dtype}")
+    post_vec, post_num, post_eps = post if post is not None else (None, 1.0, 0.0)
+    gain_vec, gain_num, eps = gain
+    vecs = [v for v in (post_vec, gain_vec) if v is not None]
+    if len({v.dtype for v in vecs}) > 1:
+        raise KernelError("normed_add_rmsnorm: the two gain vectors differ in dtype")
+    out = torch.empty((n, dim), dtype=out_dtype, device=residual.device)
+    _call("elementwise", "fms_normed_add_rmsnorm", _ptr(residual), _ptr(delta), 0 if post is None else 1, _ptr(post_vec),
+          float(post_num), float(post_eps), _ptr(gain_vec), float(gain_num), float(eps),
+          _code(vecs[0].dtype) if vecs else F32, _ptr(out), _code(out_dtype), _ptr(rows), n, dim, residual.shape[0],
+          _stream())
+    return out
+
+
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """residual (float32, in place) += delta; returns gain * rmsnorm(residual) in ``out_dtype``.  With
@@ -479,6 +530,155 @@ def decode_advance(positions: torch.Tensor, lengths: torch.Tensor, offsets: Opti
     position 0 every step."""
     _call("elementwise", "fms_decode_advance", _ptr(positions), _ptr(lengths), _ptr(offsets), _ptr(position_ids),
           _ptr(slots), int(spare_slot), positions.shape[0], _stream())
+
+
+# ---- recurrence --------------------------------------------------------------------------------------
+_recurrent_chunk = None
+SCAN_CHUNKS_FROM = 192  # tokens of a sequence in one step from which its scan runs chunk by chunk
+
+
+def mingru_scan(proj: torch.Tensor, state: torch.Tensor, batch, width: int, writes_state: bool = True) -> torch.Tensor:
+    """The minGRU recurrence over a step's rows.  ``proj`` [tokens, 3 width] = [z logits | u | g]; ``state``
+    [slots, width] float32 is read for every sequence of the batch and, with ``writes_state``, left at its value after
+    the step's last token.  Returns S_t * silu(g) [tokens, width] in proj's dtype."""
+    global _recurrent_chunk
+    n = proj.shape[0]
+    if proj.shape[1] != 3 * width or state.dtype != torch.float32 or state.shape[1] != width:
+        raise KernelError("mingru_scan: proj is [tokens, 3 width], the state float32 [slots, width]")
+    y = torch.empty((n, width), dtype=proj.dtype, device=proj.device)
+    chunk_rows = first_chunk = ab = None
+    n_chunks = 0
+    if batch.max_new >= SCAN_CHUNKS_FROM:
+        if _recurrent_chunk is None:
+            _recurrent_chunk = int(load_library("recurrent").fms_recurrent_chunk_tokens())
+        chunk_rows, first_chunk = batch.row_chunks(_recurrent_chunk)
+        n_chunks = chunk_rows.shape[0]
+        ab = torch.empty((n_chunks, 2, width), dtype=torch.float32, device=proj.device)
+    _call("recurrent", "fms_mingru_scan", _ptr(proj), _code(proj.dtype), _ptr(state), _ptr(y), _ptr(batch.first_row),
+          _ptr(batch.slots), batch.n_seqs, width, state.shape[0], 1 if writes_state else 0, _ptr(chunk_rows),
+          _ptr(first_chunk), n_chunks, _ptr(ab), _stream())
+    global launches
+    launches += 2 if n_chunks else 0
+    return y
+
+
+# ---- groups of rows, each with a matrix of its own ---------------------------------------------------
+GROUPED_FEW_ROWS = 32  # rows up to which the ragged product goes row by row
+
+
+def grouped_linear(x: torch.Tensor, weight: torch.Tensor, groups: int, rows: int, n_out: int, k: int, x_row_stride: int,
+                   x_group_offset: int, y: torch.Tensor, y_row_stride: int, y_group_offset: int) -> torch.Tensor:
+    """Uniform groups: for every group g, y[r, g * y_group_offset + :n_out] = x[r, g * x_group_offset + :k] . weight[g]^T
+    for r < rows (x and y are walked by their row strides; weight [groups, n_out, k])."""
+    if weight.dtype != x.dtype or y.dtype != x.dtype or tuple(weight.shape) != (groups, n_out, k):
+        raise KernelError(f"grouped_linear: x {x.dtype}, weight {weight.dtype} {tuple(weight.shape)}, y {y.dtype}")
+    _call("grouped", "fms_grouped_linear", _ptr(x), _ptr(weight), _ptr(y), _code(x.dtype), None, None, None, groups, rows,
+          n_out, k, x_row_stride, x_group_offset, y_row_stride, y_group_offset, 0, 0.0, 0.0, 0, _stream())
+    return y
+
+
+class Routing:
+    """What ``route`` leaves on the device: each pair's expert and weight, the experts' row ranges in the sorted
+    matrix, and the sorted, weighted rows themselves."""
+
+    __slots__ = ("expert", "weight", "offsets", "tile_first", "row_of_pair", "group_of_row", "rows", "top", "experts")
+
+
+def route(x: torch.Tensor, router: torch.Tensor, top: int) -> Routing:
+    """Scores sigmoid(x router^T) in float32; every token's ``top`` best experts; rows weight * x[token] sorted by
+    expert."""
+    n, dim = x.shape
+    experts = router.shape[0]
+    dev = x.device
+    r = Routing()
+    r.top, r.experts = top, experts
+    ints = torch.empty((n * top * 3 + 3 * (experts + 1),), dtype=torch.int32, device=dev)
+    r.expert = ints[: n * top].view(n, top)
+    r.row_of_pair = ints[n * top: 2 * n * top]
+    r.group_of_row = ints[2 * n * top: 3 * n * top]
+    o = 3 * n * top
+    counts = ints[o: o + experts + 1]
+    r.offsets = ints[o + experts + 1: o + 2 * (experts + 1)]
+    r.tile_first = ints[o + 2 * (experts + 1): o + 3 * (experts + 1)]
+    r.weight = torch.empty((n, top), dtype=torch.float32, device=dev)
+    r.rows = torch.empty((n * top, dim), dtype=x.dtype, device=dev)
+    _call("grouped", "fms_route", _ptr(x), _code(x.dtype), _ptr(router), _code(router.dtype), _ptr(r.expert),
+          _ptr(r.weight), _ptr(counts), _ptr(r.offsets), _ptr(r.tile_first), _ptr(r.row_of_pair), _ptr(r.group_of_row),
+          _ptr(r.rows), n, dim, experts, top, _stream())
+    global launches
+    launches += 2
+    return r
+
+
+def routed_linear(rows: torch.Tensor, weight: torch.Tensor, routing: Routing, glu: bool = False, limit: float = 0.0,
+                  alpha: float = 1.0) -> torch.Tensor:
+    """Ragged groups: y[r] = rows[r] . weight[expert of r]^T; with ``glu`` weight[e] = [gate; up] and
+    y = g * sigmoid(alpha g) * (u + 1) for g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    n, k = rows.shape
+    n_out = weight.shape[1] // (2 if glu else 1)
+    if weight.dtype != rows.dtype or weight.shape[0] != routing.experts or weight.shape[2] != k:
+        raise KernelError(f"routed_linear: rows {rows.dtype} {tuple(rows.shape)}, weight {weight.dtype} {tuple(weight.shape)}")
+    y = torch.empty((n, n_out), dtype=rows.dtype, device=rows.device)
+    _call("grouped", "fms_grouped_linear", _ptr(rows), _ptr(weight), _ptr(y), _code(rows.dtype), _ptr(routing.offsets),
+          _ptr(routing.tile_first), _ptr(routing.group_of_row), routing.experts, n, n_out, k, k, 0, n_out, 0,
+          1 if glu else 0, float(limit), float(alpha), 1 if n <= GROUPED_FEW_ROWS else 0, _stream())
+    return y
+
+
+def route_gather(ys: torch.Tensor, routing: Routing) -> torch.Tensor:
+    """out[token] = the sum of its pairs' rows of ``ys``, float32, in the order of its choices."""
+    n = ys.shape[0] // routing.top
+    out = torch.empty((n, ys.shape[1]), dtype=ys.dtype, device=ys.device)
+    _call("grouped", "fms_route_gather", _ptr(ys), _code(ys.dtype), _ptr(routing.row_of_pair), _ptr(out), n, ys.shape[1],
+          routing.top, _stream())
+    return out
+
+
+# ---- attention over cached latents -------------------------------------------------------------------
+_latent_split = None
+
+
+def latent_prepare(proj: torch.Tensor, q_full: torch.Tensor, c_gain: torch.Tensor, eps: float, inv_freq: torch.Tensor,
+                   rot_dims: int, batch, view, heads: int, dim: int, rot: int, rank: int, writes_cache: bool = True) -> None:
+    """From the fused projection [q heads (dim + rot each) | c (rank) | kr (rot) | ...] of a step's rows: norms c,
+    rotates kr and every head's rot part by the row's position, writes [c | kr] into the cache at the row's place and
+    the rotated query parts into q_full[:, h, rank:]."""
+    if view.keys.dtype != proj.dtype or q_full.dtype != proj.dtype:
+        raise KernelError(f"cache is {view.keys.dtype}, activations are {proj.dtype}")
+    _call("latent_attention", "fms_latent_prepare", _ptr(proj), _code(proj.dtype), proj.shape[1], _ptr(q_full), _ptr(c_gain),
+          _code(c_gain.dtype), float(eps), _ptr(inv_freq), int(rot_dims), _ptr(batch.positions),
+          _ptr(getattr(batch, "position_ids", None)), _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys),
+          _ptr(view.table), view.table.shape[1], view.block_tokens, proj.shape[0], heads, dim, rot, rank,
+          1 if writes_cache else 0, batch.slots.shape[0], view.table.shape[0], view.keys.shape[0],
+          _ptr(error_flag(proj.device)), _stream())
+
+
+def latent_attention(q_full: torch.Tensor, batch, view, gate: Optional[torch.Tensor], gate_offset: int,
+                     sink: Optional[torch.Tensor], heads: int, rank: int, rot: int, scale: float) -> torch.Tensor:
+    """Causal softmax attention of the step's rows over the cached latent rows [c | kr] (which already hold the step's
+    own), with a per-head sink in the denominator and a per-head sigmoid gate on the result.  ``gate``: the matrix
+    whose column ``gate_offset + h`` holds head h's gate logit of each row.  Returns [tokens, heads, rank]."""
+    global _latent_split
+    n = q_full.shape[0]
+    out = torch.empty((n, heads, rank), dtype=q_full.dtype, device=q_full.device)
+    n_splits, part_o, part_ml = 1, None, None
+    if batch.decode:
+        if _latent_split is None:
+            _latent_split = int(load_library("latent_attention").fms_latent_split_tokens())
+        n_splits = max(1, (batch.max_len_after + _latent_split - 1) // _latent_split)
+        if n_splits > 1:
+            part_o = torch.empty((n, heads, n_splits, rank), dtype=torch.float32, device=q_full.device)
+            part_ml = torch.empty((n, heads, n_splits, 2), dtype=torch.float32, device=q_full.device)
+    gate_ptr = None if gate is None else _ptr(gate) + gate_offset * gate.element_size()
+    _call("latent_attention", "fms_latent_attention", _ptr(q_full), _ptr(out), _code(q_full.dtype), _ptr(view.keys), gate_ptr,
+          0 if gate is None else gate.shape[1], _ptr(sink), _code(sink.dtype) if sink is not None else F32,
+          _ptr(view.table), view.table.shape[1], view.block_tokens, _ptr(batch.slots), _ptr(batch.token_seq),
+          _ptr(batch.positions), n, n_splits, _ptr(part_o), _ptr(part_ml), heads, rank, rot, float(scale),
+          batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())
+    if n_splits > 1:
+        global launches
+        launches += 1
+    return out
 
 
 # ---- sampling ----------------------------------------------------------------------------------------

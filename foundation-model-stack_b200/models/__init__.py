@@ -101,7 +101,8 @@ def get_model(architecture: str, variant: Optional[str] = None, model_path: Opti
             raise ValueError("hf_pretrained needs a model_path with a config.json")
         values = read_config_json(model_path)
         if architecture == "hf_pretrained":
-            names = values.get("architectures") or [None]
+            # the name under "architectures" (a list, as transformers writes it) or under "architecture"
+            names = values.get("architectures") or [values.get("architecture")]
             if names[0] not in _hf_architectures:
                 raise KeyError(f"config.json names architecture {names[0]!r}; known: {sorted(_hf_architectures)}")
             architecture = _hf_architectures[names[0]]
@@ -133,6 +134,7 @@ def get_model(architecture: str, variant: Optional[str] = None, model_path: Opti
 
 
 from . import llama  # noqa: E402,F401  (registers the architecture and its variants)
+from . import goletar  # noqa: E402,F401
 
 
 def _import_plugins() -> None:

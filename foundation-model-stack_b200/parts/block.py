@@ -11,11 +11,17 @@ Interface of a block (what the decoder calls); ``BlockSpec.arrangement`` names t
         residual [tokens, dim] float32, updated in place; pending [tokens, dim] in the compute dtype or None
 
 ``PreNormBlock`` ("pre_norm", fms/models/llama.py:118-167): x += mixer(norm(x)); x += feed_forward(norm(x)).
+
+``SandwichBlock`` ("sandwich"): a norm before and after each sublayer, x += post1(mixer(pre1(x)));
+x += post2(feed_forward(pre2(x))).  What it hands on as pending is a ``NormedDelta``: the next norm (this layer's, the
+next layer's or the decoder's last) norms it, adds it and takes its own norm in one kernel.  A layer without a
+feed-forward ends after its mixer.
 """
 from __future__ import annotations
 
 from ..config.specs import BlockSpec
 from .base import Part
+from .norm import NormedDelta
 from .registry import build_feed_forward, build_mixer, build_norm, register_block
 
 
@@ -38,5 +44,35 @@ class PreNormBlock(Part):
         return self.feed_forward.forward(h)
 
 
+class SandwichBlock(Part):
+    def __init__(self, spec: BlockSpec) -> None:
+        super().__init__()
+        n_mixer_norm, n_mixer, n_ff_norm, n_ff = spec.names
+        n_mixer_post, n_ff_post = spec.post_names
+        if spec.mixer_post_norm is None or (spec.feed_forward is not None and (
+                spec.feed_forward_norm is None or spec.feed_forward_post_norm is None)):
+            raise ValueError("a sandwich layer needs a norm before and after each of its sublayers")
+        self.mixer_norm = self.add(n_mixer_norm, build_norm(spec.mixer_norm))
+        self.mixer = self.add(n_mixer, build_mixer(spec.mixer))
+        self.mixer_post_norm = self.add(n_mixer_post, build_norm(spec.mixer_post_norm))
+        self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm = self.add(n_ff_norm, build_norm(spec.feed_forward_norm))
+            self.feed_forward = self.add(n_ff, build_feed_forward(spec.feed_forward))
+            self.feed_forward_post_norm = self.add(n_ff_post, build_norm(spec.feed_forward_post_norm))
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, residual, pending, batch, cache_view, writes_cache, dtype):
+        h = self.mixer_norm.apply(residual, pending, dtype)
+        pending = NormedDelta(self.mixer.forward(h, batch, cache_view, writes_cache), self.mixer_post_norm)
+        if self.feed_forward is None:
+            return pending
+        h = self.feed_forward_norm.apply(residual, pending, dtype)
+        return NormedDelta(self.feed_forward.forward(h), self.feed_forward_post_norm)
+
+
 Block = PreNormBlock  # the name under which earlier callers know it
 register_block("pre_norm", PreNormBlock)
+register_block("sandwich", SandwichBlock)

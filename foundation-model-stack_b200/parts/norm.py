@@ -10,6 +10,14 @@ Interface of a norm (what a block and the decoder call):
 sublayer's output, which the norm first adds to the stream in place, in float32: the residual sum and
 the norm are one pass over the row.  With ``rows`` only those rows are normed and returned and the
 stream is left as it is (used before the output head).
+
+``delta`` may also be a ``NormedDelta``: a sublayer's output that is itself normed before it is added (a layer with a
+norm after each sublayer as well as before it).  The adding norm then does both in one kernel:
+d = post_norm(delta); residual += d; out = norm(residual), all float32.
+
+``ScalarRMSNorm`` ("rmsnorm_scalar"): y = g * x / sqrt(mean(x^2) + eps) with ONE number g for the whole row (a tensor
+without dimensions in the checkpoint).  The number is read once when the weights are loaded and handed to the kernel
+by value.
 """
 from __future__ import annotations
 
@@ -19,6 +27,17 @@ from .base import Part
 from .registry import register_norm
 
 
+class NormedDelta:
+    """A sublayer's output ``delta`` that ``norm`` (an RMS norm of this module) is applied to before it is added to the
+    residual stream; the norm that adds it does so."""
+
+    __slots__ = ("delta", "norm")
+
+    def __init__(self, delta, norm) -> None:
+        self.delta = delta
+        self.norm = norm
+
+
 class RMSNorm(Part):
     def __init__(self, spec: NormSpec) -> None:
         super().__init__()
@@ -26,11 +45,43 @@ class RMSNorm(Part):
         self.eps = float(spec.eps)
         self.declare("weight", (spec.dim,), role="vector")
 
+    def gain(self):
+        """(vector or None, the one number where there is no vector, eps): what the fused kernel takes."""
+        return self.tensor("weight"), 1.0, self.eps
+
     def apply(self, residual, delta, out_dtype, rows=None):
+        if isinstance(delta, NormedDelta):
+            return ops.normed_add_rmsnorm(residual, delta.delta, delta.norm.gain(), self.gain(), out_dtype, rows)
         return ops.add_rmsnorm(residual, delta, self.tensor("weight"), self.eps, out_dtype, rows)
 
     def kernel_libraries(self, dtype):
         return ["elementwise"]
 
 
+class ScalarRMSNorm(Part):
+    def __init__(self, spec: NormSpec) -> None:
+        super().__init__()
+        self.dim = spec.dim
+        self.eps = float(spec.eps)
+        self.declare("weight", (), role="vector")
+        self._gain = None
+
+    def finalize(self, device, dtype) -> None:
+        super().finalize(device, dtype)
+        self._gain = float(self.tensor("weight").float().item())
+
+    def gain(self):
+        return None, self._gain, self.eps
+
+    def apply(self, residual, delta, out_dtype, rows=None):
+        post = None
+        if isinstance(delta, NormedDelta):
+            delta, post = delta.delta, delta.norm.gain()
+        return ops.normed_add_rmsnorm(residual, delta, post, self.gain(), out_dtype, rows)
+
+    def kernel_libraries(self, dtype):
+        return ["elementwise"]
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("rmsnorm_scalar", ScalarRMSNorm)

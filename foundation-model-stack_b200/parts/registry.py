@@ -7,7 +7,8 @@ from __future__ import annotations
 
 from typing import Callable, Dict
 
-_REGISTRIES: Dict[str, Dict[str, Callable]] = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}}
+_REGISTRIES: Dict[str, Dict[str, Callable]] = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {},
+                                               "embedding": {}}
 
 
 def _register(family: str, kind: str, factory: Callable, replace: bool = False) -> None:
@@ -44,6 +45,18 @@ def register_feed_forward(kind, factory, replace=False):
 def register_block(arrangement, factory, replace=False):
     """``arrangement``: the value of ``BlockSpec.arrangement`` that this class builds."""
     _register("block", arrangement, factory, replace)
+
+
+def register_embedding(kind, factory, replace=False):
+    """``factory(spec, vocab_size, dim)`` builds the part that turns a step's token ids into rows of the stream."""
+    _register("embedding", kind, factory, replace)
+
+
+def build_embedding(spec, vocab_size: int, dim: int):
+    table = _REGISTRIES["embedding"]
+    if spec.kind not in table:
+        raise KeyError(f"no embedding of kind {spec.kind!r} is registered; known: {sorted(table)}")
+    return table[spec.kind](spec, vocab_size, dim)
 
 
 def build_block(spec):
