@@ -1,5 +1,6 @@
 from .model_config import ModelConfig
-from .specs import BlockSpec, DecoderSpec, FeedForwardSpec, LayerCall, MixerSpec, NormSpec, PositionSpec
+from .specs import (BlockSpec, DecoderSpec, EmbeddingSpec, FeedForwardSpec, LayerCall, MixerSpec, NormSpec,
+                    PositionSpec)
 
-__all__ = ["ModelConfig", "BlockSpec", "DecoderSpec", "FeedForwardSpec", "LayerCall", "MixerSpec", "NormSpec",
-           "PositionSpec"]
+__all__ = ["ModelConfig", "BlockSpec", "DecoderSpec", "EmbeddingSpec", "FeedForwardSpec", "LayerCall", "MixerSpec",
+           "NormSpec", "PositionSpec"]

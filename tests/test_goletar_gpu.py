@@ -1,0 +1,435 @@
+"""The Goletar design on the GPU against its plain restatement (tests/plain_goletar.py): every mechanism alone, then
+whole models of several shapes through the engine — prompts, token-by-token decoding (graphs included), prompts cut
+into portions, unequal batches, slots and blocks that are used again, long decoding over the edges of cache blocks
+and of the decode kernel's key splits, greedy generation and the trace program."""
+import io
+import json
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import goletar_models as gm
+import plain_goletar as pg
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = {"fp32": torch.float32, "bf16": torch.bfloat16}
+
+
+def _weights(which, mild):
+    """Sharp weights for the float32 comparisons (peaked attention rows, saturated gates: a dropped key or a wrong
+    clamp shows), mild ones for bfloat16, where 16-bit rounding of scores of magnitude ten would itself move the
+    softmax by several percent."""
+    i = list(gm.CONFIGS).index(which)
+    if mild:
+        return gm.tensors(gm.CONFIGS[which], seed=31 + i, std=0.02, router_std=0.6, sink_std=0.5)
+    return gm.tensors(gm.CONFIGS[which], seed=11 + i)
+
+
+def K(which, dtype):
+    return which + ("_mild" if dtype == "bf16" else "")
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("goletar")
+    out = {}
+    for which, cfg in gm.CONFIGS.items():
+        out[which] = gm.write_folder(str(root / which), cfg, _weights(which, False))
+        out[which + "_mild"] = gm.write_folder(str(root / (which + "_mild")), cfg, _weights(which, True))
+    return out
+
+
+@pytest.fixture(scope="module")
+def oracles():
+    out = {}
+    for which, cfg in gm.CONFIGS.items():
+        out[which] = pg.PlainGoletar(cfg, _weights(which, False))
+        out[which + "_mild"] = pg.PlainGoletar(cfg, _weights(which, True))
+    return out
+
+
+_models = {}
+
+
+def model_of(folders, which, dtype):
+    from fms_b200.models import get_model
+
+    key = (which, dtype)
+    if key not in _models:
+        _models[key] = get_model("hf_pretrained", model_path=folders[K(which, dtype)], device_type="cuda", data_type=dtype)
+    return _models[key]
+
+
+def close(got, want, dtype, margin=None):
+    """float32: every element.  bfloat16 with ``margin`` (per row, from the oracle: how far the routing of the row's
+    token is from a close call): rows whose own routing is a close call are left out, and of the others 97 in 100
+    must be within the tolerance — a token that 16-bit rounding sends to another expert also shifts what later rows
+    read from the cache and the recurrence, so single later rows may differ; float32 is the sharp comparison."""
+    want = want.to(torch.float64)
+    got = got.detach().cpu().to(torch.float64)
+    assert torch.isfinite(got).all()
+    top = want.abs().max().item()
+    if dtype == "fp32":
+        torch.testing.assert_close(got, want, atol=3e-5 * max(1.0, top), rtol=1e-4)
+    elif margin is None:
+        torch.testing.assert_close(got, want, atol=0.03 * top, rtol=0.03)
+    else:
+        keep = margin > 0.03
+        within = ((got - want).abs() <= 0.03 * top + 0.03 * want.abs()).all(-1)
+        if len(keep) >= 20:
+            assert keep.float().mean() > 0.5 and within[keep].float().mean() >= 0.97, (keep.float().mean(), within[keep].float().mean())
+        else:
+            assert within[keep].all()
+
+
+# ---- mechanisms alone ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("dim", [36, 256, 1000])
+def test_norm_of_a_normed_delta(dtype, dim):
+    from fms_b200.kernels import ops
+
+    dt = DTYPES[dtype]
+    g = torch.Generator().manual_seed(dim)
+    res = torch.randn(7, dim, generator=g) * 3
+    delta = (torch.randn(7, dim, generator=g) * 5).to(dt)
+    vec = (0.5 + torch.rand(dim, generator=g)).to(dt)
+    for post, gain in (((None, 1.7, 1e-3), (None, 0.6, 1e-5)), ((vec, 1.0, 1e-5), (None, 2.0, 1e-6)),
+                       (None, (vec, 1.0, 1e-5)), ((None, 0.3, 1e-2), (vec, 1.0, 1e-4))):
+        def plain(x, spec):
+            v, num, eps = spec
+            return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * (v.double() if v is not None else num)
+
+        d = delta.double() if post is None else plain(delta.double(), post)
+        want_res = res.double() + d
+        to_dev = lambda s: None if s is None else (None if s[0] is None else s[0].cuda(), s[1], s[2])
+        r = res.clone().cuda()
+        out = ops.normed_add_rmsnorm(r, delta.cuda(), to_dev(post), to_dev(gain), dt)
+        close(r, want_res, "fp32")
+        close(out, plain(want_res, gain), dtype)
+        rows = torch.tensor([5, 0, 5], dtype=torch.int32).cuda()
+        r2 = res.clone().cuda()
+        out = ops.normed_add_rmsnorm(r2, delta.cuda(), to_dev(post), to_dev(gain), dt, rows)
+        assert torch.equal(r2.cpu(), res)  # with rows the stream stays as it is
+        close(out, plain(want_res, gain)[[5, 0, 5]], dtype)
+
+
+def part_with(part, tensors, dtype):
+    for q, owner, local, decl in part.named_decls():
+        owner.set_tensor(local, tensors[q].to(device="cuda", dtype=dtype).contiguous())
+    part.finalize(torch.device("cuda"), dtype)
+    return part
+
+
+def step_through(mixer, x, cuts, dtype):
+    """Runs x [n, dim] through a mixer as ONE sequence cut into steps of the given sizes."""
+    from fms_b200.cache import Cache
+    from fms_b200.engine.batch import Batch
+
+    cache = Cache([mixer.cache_request()], max_tokens=1024, max_positions=1024, dtype=dtype, device="cuda")
+    (slot,) = cache.begin(1)
+    out, at = [], 0
+    for n in cuts:
+        before = cache.prepare([slot], [n])
+        batch = Batch.from_lists([slot], before, [[0] * n], [[]], "cuda")
+        out.append(mixer.forward(x[at:at + n].contiguous(), batch, cache.layer_view(0), True))
+        cache.commit([slot], [n])
+        at += n
+    assert at == x.shape[0]
+    return torch.cat(out)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_mingru_alone_whole_in_portions_and_in_chunks(dtype):
+    from fms_b200.config import MixerSpec
+    from fms_b200.parts import build_mixer
+
+    dt, dim, width, n = DTYPES[dtype], 40, 56, 451
+    g = torch.Generator().manual_seed(5)
+    w = {k: (torch.randn(*s, generator=g) * sd).to(torch.bfloat16) for k, s, sd in (
+        ("z", (width, dim), 0.4), ("zb", (width,), 1.0), ("x", (width, dim), 0.4), ("xb", (width,), 1.0),
+        ("g", (width, dim), 0.4), ("o", (dim, width), 0.2))}
+    mixer = part_with(build_mixer(MixerSpec("mingru", dim=dim, options=(("width", width),))), {
+        "zxg_fused.weight": torch.cat([w["z"], w["x"], w["g"]]),
+        "zxg_fused.bias": torch.cat([w["zb"], w["xb"], torch.zeros(width, dtype=torch.bfloat16)]),
+        "dense.weight": w["o"]}, dt)
+    x = (torch.randn(n, dim, generator=g)).to(dt)
+    d = {k: v.double() for k, v in w.items()}
+    want = pg.mingru(x.double(), d["z"], d["zb"], d["x"], d["xb"], d["g"], d["o"])
+    # whole (chunk by chunk), portions down to two tokens and one, and a long portion after short ones
+    for cuts in ([n], [2, 1, 1, 3, 60, 64, 65, 255], [7, 193, 251], [1] * 9 + [442]):
+        close(step_through(mixer, x.cuda(), cuts, dt), want, dtype)
+
+
+def latent_tensors(g, dim_in, m, std=0.3):
+    h, dim, rot, v, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    mk = lambda *s, sd=std: (torch.randn(*s, generator=g) * sd).to(torch.bfloat16)
+    return {"q": mk(h * (dim + rot), dim_in), "dkv": mk(r + rot, dim_in), "norm": (0.5 + torch.rand(r, generator=g)).to(torch.bfloat16),
+            "uk": mk(h * dim, r), "uv": mk(h * v, r, sd=0.1), "sink": mk(h, sd=1.0), "g": mk(h, dim_in), "o": mk(dim_in, h * v, sd=0.1)}
+
+
+def latent_mixer(m, dim_in, w, eps, dt):
+    from fms_b200.config import MixerSpec, PositionSpec
+    from fms_b200.parts import build_mixer
+
+    spec = MixerSpec("latent_attention", dim=dim_in, nheads=m["heads"], kvheads=1, head_dim=m["dim"], scale=m["scale"],
+                     position=PositionSpec("rope", head_dim=m["rot"]["dims"], theta=m["rot"]["base"]),
+                     options=(("rot", m["rot_dim"]), ("vdim", m["vdim"]), ("rank", m["kv_rank"]),
+                              ("rot_dims", m["rot"]["dims"]), ("eps", eps)))
+    return part_with(build_mixer(spec), {"in_proj.weight": torch.cat([w["q"], w["dkv"], w["g"]]), "latent_norm": w["norm"],
+                                         "sink": w["sink"], "uk": w["uk"], "uv": w["uv"], "dense.weight": w["o"]}, dt)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("shape", [(3, 16, 8, 12, 24, 8), (9, 6, 2, 5, 10, 2), (2, 32, 16, 64, 130, 6), (1, 0, 8, 8, 8, 8)])
+def test_latent_attention_alone(dtype, shape):
+    heads, dim, rot, vdim, rank, dims = shape
+    m = gm.latent(heads, dim, rot, vdim, rank, 300.0, None, rot_dims=dims)["mixer"]
+    dt, dim_in, n = DTYPES[dtype], 40, 331
+    g = torch.Generator().manual_seed(sum(shape))
+    w = latent_tensors(g, dim_in, m)
+    mixer = latent_mixer(m, dim_in, w, 1e-5, dt)
+    x = torch.randn(n, dim_in, generator=g).to(dt)
+    d = {k: v.double() for k, v in w.items()}
+    want, _ = pg.latent_attention(x.double(), m, 1e-5, d["q"], d["dkv"], d["norm"], d["uk"], d["uv"], d["sink"], d["g"], d["o"])
+    # whole; portions whose edges fall on and beside the cache's blocks of 64; the last rows one by one (the decode
+    # kernel, over the edge of its first split of 256 keys)
+    for cuts in ([n], [63, 1, 1, 63, 2, 128, 73], [250] + [1] * 81):
+        close(step_through(mixer, x.cuda(), cuts, dt), want, dtype)
+
+
+def test_latent_attention_sink_and_a_far_key():
+    """Weights made so that a fault shows: head 0's sink is so large that it takes all of the softmax, head 1's
+    so small that it takes nothing, and the keys' rotated part is scaled up so that every query has a few keys far
+    back that hold most of its weight."""
+    m = gm.latent(2, 8, 8, 8, 16, 50.0, None)["mixer"]
+    g = torch.Generator().manual_seed(77)
+    w = latent_tensors(g, 32, m)
+    w["sink"] = torch.tensor([200.0, -200.0]).to(torch.bfloat16)
+    w["dkv"][m["kv_rank"]:] *= 6
+    mixer = latent_mixer(m, 32, w, 1e-5, torch.float32)
+    x = torch.randn(600, 32, generator=g)
+    d = {k: v.double() for k, v in w.items()}
+    want, p = pg.latent_attention(x.double(), m, 1e-5, d["q"], d["dkv"], d["norm"], d["uk"], d["uv"], d["sink"], d["g"], d["o"])
+    far = p[1, 300:, :200].sum(-1)  # head 1: weight on keys at least 100 back
+    assert (far > 0.5).sum() > 20 and p[0].sum(-1).max() < 1e-9 and p[1, 5:].sum(-1).min() > 0.999
+    for cuts in ([600], [520] + [1] * 80):
+        close(step_through(mixer, x.cuda(), cuts, torch.float32), want, "fp32")
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("n_experts,top,rows", [(5, 1, 70), (5, 2, 3), (8, 3, 200), (4, 4, 33), (16, 2, 1)])
+def test_routed_experts_alone(dtype, n_experts, top, rows):
+    from fms_b200.config import FeedForwardSpec
+    from fms_b200.parts import build_feed_forward
+
+    dt, dim, ff, limit = DTYPES[dtype], 48, 20, 0.75
+    g = torch.Generator().manual_seed(n_experts * 10 + top)
+    mk = lambda *s, sd: (torch.randn(*s, generator=g) * sd).to(torch.bfloat16)
+    router = mk(n_experts, dim, sd=0.5)
+    gates, ups, downs = ([mk(*s, sd=0.3) for _ in range(n_experts)] for s in ((ff, dim), (ff, dim), (dim, ff)))
+    part = part_with(build_feed_forward(FeedForwardSpec("routed_experts", dim=dim, hidden=ff, options=(
+        ("experts", n_experts), ("top", top), ("limit", limit), ("alpha", 1.702)))), {
+        "router.weight": router, "gate_up": torch.stack([torch.cat([a, b]) for a, b in zip(gates, ups)]),
+        "down": torch.stack(downs)}, dt)
+    x = torch.randn(rows, dim, generator=g).to(dt)
+    want, _ = pg.routed_experts(x.double(), router.double(), [t.double() for t in gates], [t.double() for t in ups],
+                                [t.double() for t in downs], top, limit)
+    margin = pg.routing_margin(x.double(), router.double(), top)
+    assert margin.min() > 1e-6
+    close(part.forward(x.cuda()), want, dtype, margin)
+    # the same rows among others, in another order: a row's result is its own
+    perm = torch.randperm(rows, generator=g)
+    close(part.forward(torch.cat([x[perm], x[:1]]).cuda())[:rows], want[perm], dtype, margin[perm])
+
+
+def test_pair_hash_embedding_alone():
+    from fms_b200.cache import Cache
+    from fms_b200.config import EmbeddingSpec
+    from fms_b200.engine.batch import Batch
+    from fms_b200.parts import build_embedding
+
+    vocab, dim, buckets, mp, mc = 50000, 24, 997, 3_000_000_019, 2_000_000_011  # products beyond 64-bit? no: beyond 32
+    g = torch.Generator().manual_seed(3)
+    table, pairs = torch.randn(vocab, dim, generator=g), torch.randn(buckets + 1, dim, generator=g)
+    part = build_embedding(EmbeddingSpec("pair_hash", (("buckets", buckets), ("mul_prev", mp), ("mul_cur", mc))), vocab, dim)
+    part.set_tensor("weight", table.cuda()), part.set_tensor("pairs", pairs.cuda())
+    cache = Cache([], max_tokens=256, max_positions=256, dtype=torch.float32, device="cuda",
+                  named_requests={"embedding": part.cache_request()})
+    seqs = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in (9, 1, 14)]
+    want = [pg.pair_hash_embedding(s, table.double(), pairs.double(), buckets, mp, mc) * 2.0 for s in seqs]
+    slots = cache.begin(3)
+    got = [[], [], []]
+    # unequal portions of three sequences in each step: (4, 1, 2), then (5, -, 1), then (-, -, 11)
+    for cut in ((4, 1, 2), (5, 0, 1), (0, 0, 11)):
+        live = [i for i in range(3) if cut[i]]
+        before = [cache.length[slots[i]] for i in live]
+        toks = [seqs[i][b:b + cut[i]] for i, b in zip(live, before)]
+        cache.prepare([slots[i] for i in live], [cut[i] for i in live])
+        batch = Batch.from_lists([slots[i] for i in live], before, toks, [[] for _ in live], "cuda")
+        out = part.forward(batch, cache.layer_view("embedding"), 2.0)
+        cache.commit([slots[i] for i in live], [cut[i] for i in live])
+        for i, piece in zip(live, torch.split(out, [cut[i] for i in live])):
+            got[i].append(piece)
+    for i in range(3):
+        close(torch.cat(got[i]), want[i], "fp32")
+
+
+# ---- whole models -------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("which", ["p", "q", "r"])
+def test_whole_prompts_alone(folders, oracles, which, dtype):
+    model = model_of(folders, which, dtype)
+    engine = model.new_engine(max_tokens=1024, sampling=False)
+    for i, n in enumerate((1, 2, 63, 64, 65, 300)):
+        ids = gm.prompt(gm.CONFIGS[which], n, i)
+        (slot,) = engine.begin(1)
+        got = engine.step([slot], [ids], [list(range(n))])
+        engine.release([slot])
+        want = oracles[K(which, dtype)].logits(ids)
+        close(got, want, dtype, oracles[K(which, dtype)].margin)
+    engine.check()
+    assert engine.cache.slots.n_held == 0 and all(g.pool.n_held == 0 for g in engine.cache.groups if hasattr(g, "pool"))
+
+
+@pytest.mark.parametrize("which,dtype", [("p", "fp32"), ("q", "fp32"), ("r", "bf16")])
+def test_token_by_token_from_the_first_token(folders, oracles, which, dtype):
+    """Decode steps from a sequence's very first token (the first plain, the second captured, the rest replayed), over
+    the edge of a cache block, twice in the same slot."""
+    engine = model_of(folders, which, dtype).new_engine(max_tokens=256, sampling=False)
+    for rep in range(2):
+        ids = gm.prompt(gm.CONFIGS[which], 70, 20 + rep)
+        (slot,) = engine.begin(1)
+        got = torch.cat([engine.step([slot], [[t]], [[0]]) for t in ids])
+        engine.release([slot])
+        want = oracles[K(which, dtype)].logits(ids)
+        close(got, want, dtype, oracles[K(which, dtype)].margin)
+    assert engine.graphs_captured >= 1
+    engine.check()
+
+
+@pytest.mark.parametrize("which,dtype", [("p", "fp32"), ("q", "bf16"), ("r", "fp32")])
+def test_prompt_then_long_decoding_over_split_edges(folders, oracles, which, dtype):
+    """A prompt of 250 tokens, then 290 tokens one by one: the decode kernel goes from one split of 256 keys to two and
+    to three, the cache from its fourth block to its ninth."""
+    engine = model_of(folders, which, dtype).new_engine(max_tokens=1024, sampling=False)
+    ids = gm.prompt(gm.CONFIGS[which], 540, 31)
+    (slot,) = engine.begin(1)
+    got = [engine.step([slot], [ids[:250]], [list(range(250))])]
+    got += [engine.step([slot], [[t]], [[0]]) for t in ids[250:]]
+    engine.release([slot])
+    want = oracles[K(which, dtype)].logits(ids)
+    close(torch.cat(got), want, dtype, oracles[K(which, dtype)].margin)
+    engine.check()
+
+
+@pytest.mark.parametrize("which,dtype", [("p", "fp32"), ("q", "fp32"), ("r", "fp32"), ("p", "bf16")])
+def test_prompts_cut_into_portions(folders, oracles, which, dtype):
+    engine = model_of(folders, which, dtype).new_engine(max_tokens=1024, sampling=False)
+    ids = gm.prompt(gm.CONFIGS[which], 420, 41)
+    want = oracles[K(which, dtype)].logits(ids)
+    margin = oracles[K(which, dtype)].margin
+    for cuts in ([2, 3, 59, 1, 64, 65, 6, 220], [193, 2, 225], [1, 1, 2, 416]):
+        (slot,) = engine.begin(1)
+        got, at = [], 0
+        for n in cuts:
+            got.append(engine.step([slot], [ids[at:at + n]], [list(range(n))]))
+            at += n
+        engine.release([slot])
+        close(torch.cat(got), want, dtype, margin)
+    engine.check()
+
+
+@pytest.mark.parametrize("which,dtype", [("p", "fp32"), ("q", "fp32"), ("r", "fp32"), ("q", "bf16")])
+def test_unequal_batches_freed_slots_and_poisoned_blocks(folders, oracles, which, dtype):
+    """Requests of unequal lengths start together and go on one token at a time while the shorter ones end; then
+    everything the cache holds is filled with NaN (keys, states) or junk (the last tokens) and new requests take the
+    freed slots and blocks.  Every request against the oracle, alone."""
+    cfg = gm.CONFIGS[which]
+    engine = model_of(folders, which, dtype).new_engine(max_tokens=64 * 12, max_slots=5, sampling=False)
+    for round_ in range(2):
+        lengths, extra = ((1, 70, 5, 131, 64), (3, 9, 0, 12, 12)) if round_ == 0 else ((128, 2, 33), (5, 5, 1))
+        full = [gm.prompt(cfg, n + e, 50 + 10 * round_ + i) for i, (n, e) in enumerate(zip(lengths, extra))]
+        slots = engine.begin(len(lengths))
+        got = [[] for _ in lengths]
+        first = engine.step(slots, [f[:n] for f, n in zip(full, lengths)], [list(range(n)) for n in lengths])
+        for i, piece in enumerate(torch.split(first, list(lengths))):
+            got[i].append(piece)
+        for t in range(max(extra)):
+            live = [i for i in range(len(lengths)) if t < extra[i]]
+            out = engine.step([slots[i] for i in live], [[full[i][lengths[i] + t]] for i in live])
+            for i, row in zip(live, out):
+                got[i].append(row[None])
+            done = [i for i in live if t + 1 == extra[i]]
+            engine.release([slots[i] for i in done])
+        engine.release([slots[i] for i in range(len(lengths)) if extra[i] == 0])
+        for i, f in enumerate(full):
+            want = oracles[K(which, dtype)].logits(f)
+            close(torch.cat(got[i]), want, dtype, oracles[K(which, dtype)].margin if len(f) > 8 else None)
+        assert engine.cache.slots.n_held == 0
+        for g in engine.cache.groups:
+            g.storage.fill_(float("nan") if g.storage.is_floating_point() else 12345)
+    engine.check()
+
+
+def test_many_sequences_in_one_decode_step_fill_rows_and_graphs(folders, oracles):
+    """Eleven sequences decode together (filled up to twelve rows with rows in the spare slot), then nine of them."""
+    which, cfg, dtype = "p", gm.CONFIGS["p"], "fp32"
+    engine = model_of(folders, which, "fp32").new_engine(max_tokens=64 * 24, sampling=False)
+    full = [gm.prompt(cfg, 3 + 5 * i + 6, 70 + i) for i in range(11)]
+    slots = engine.begin(11)
+    engine.step(slots, [f[:-6] for f in full], [[] for _ in full])
+    got = [[] for _ in full]
+    for t in range(6):
+        live = list(range(11)) if t < 3 else list(range(2, 11))
+        out = engine.step([slots[i] for i in live], [[full[i][len(full[i]) - 6 + t]] for i in live])
+        for i, row in zip(live, out):
+            got[i].append(row[None])
+    engine.release(slots)
+    for i, f in enumerate(full):
+        want = oracles[K(which, dtype)].logits(f)
+        close(torch.cat(got[i]), want[len(f) - 6: len(f) - 6 + len(got[i])], "fp32")
+    engine.check()
+
+
+def test_greedy_generation_through_generate(folders, oracles):
+    from fms_b200.utils.generation import generate
+
+    which, cfg, dtype = "q", gm.CONFIGS["q"], "fp32"
+    model = model_of(folders, which, "fp32")
+    prompts = [gm.prompt(cfg, n, 80 + i) for i, n in enumerate((5, 1, 40))]
+    out = generate(model, [torch.tensor(p) for p in prompts], max_new_tokens=10, do_sample=False)
+    for p, o in zip(prompts, out):
+        o = o.tolist()
+        assert o[: len(p)] == p and len(o) == len(p) + 10
+        for k in range(len(p), len(o)):  # every new token is the oracle's choice given what came before
+            row = oracles[K(which, dtype)].logits(o[:k])[-1]
+            best = row.topk(2).values
+            if best[0] - best[1] > 1e-3:
+                assert o[k] == int(row.argmax())
+
+
+def test_trace_program_replays_a_batch(folders, oracles, tmp_path):
+    which, cfg, dtype = "r", gm.CONFIGS["r"], "fp32"
+    a, b = gm.prompt(cfg, 70, 90), gm.prompt(cfg, 9, 91)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:66], "want": [0, 65]}, {"id": "b", "tokens": b[:5], "want": [4]}], "end": []}]
+    for t in range(4):
+        steps.append({"step": t + 1, "entries": [{"id": "a", "tokens": [a[66 + t]], "want": [0]},
+                                                  {"id": "b", "tokens": [b[5 + t]], "want": [0] if t % 2 else []}],
+                      "end": ["a", "b"] if t == 3 else []})
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders[which], "--dtype",
+                           "float32", "--out", str(tmp_path), "--max-tokens", "256"],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(5)]
+    wa, wb = oracles[K(which, dtype)].logits(a), oracles[K(which, dtype)].logits(b)
+    read = lambda i: torch.from_numpy(np.fromfile(os.path.join(str(tmp_path), f"{i}.f32"), dtype="<f4").reshape(-1, cfg["vocab"]))
+    close(read(0), torch.stack([wa[0], wa[65], wb[4]]), "fp32")
+    for t in range(4):
+        want = [wa[66 + t]] + ([wb[5 + t]] if t % 2 else [])
+        close(read(t + 1), torch.stack(want), "fp32")
