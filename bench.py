@@ -465,6 +465,109 @@ def run_ours(args):
 
 
 # --------------------------------------------------------------------------------------------------
+# --compare goletar: the Goletar design beside Llama at equal width, layer for layer
+# --------------------------------------------------------------------------------------------------
+GOLETAR_SHAPE = dict(width=4096, recurrent_width=4096, heads=32, dim=96, rot_dim=32, vdim=128, kv_rank=512, experts=16,
+                     top=4, ff=3584, vocab=128256)
+
+
+def goletar_layers(kinds, with_experts=True):
+    from fms_b200.models.goletar import latent_layer, mingru_layer, moe
+
+    g = GOLETAR_SHAPE
+    mlp = moe(g["experts"], g["top"], g["ff"], 7.0) if with_experts else None
+    return [mingru_layer(g["recurrent_width"], mlp) if k == "mingru" else
+            latent_layer(g["heads"], g["dim"], g["rot_dim"], g["vdim"], g["kv_rank"], 10000.0, mlp) for k in kinds]
+
+
+def goletar_counts(layers, tokens, batch_context, batch):
+    """(flops of a prompt of `tokens`, bytes a decode step of `batch` sequences with `batch_context` cached tokens reads)
+    of the given layers: products, attention over the cached latents, the experts each token uses (for a decode step:
+    the distinct experts that `batch` tokens are expected to hit)."""
+    g = GOLETAR_SHAPE
+    d, flops, weights, cache = g["width"], 0.0, 0.0, 0.0
+    for layer in layers:
+        m = layer["mixer"]
+        if layer["type"] == "mingru":
+            w = 4 * m["width"] * d
+            att = 0.0
+        else:
+            h, dim, rot, v, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            w = d * (h * (dim + rot) + r + rot + h) + h * dim * r + h * v * r + h * v * d
+            att = tokens * tokens * h * (2 * r + rot)  # causal half of 2 T^2 (width + rank) a head
+            cache += batch_context * (r + rot) * 2
+        flops += 2 * tokens * w + att
+        weights += 2 * w
+        if layer.get("mlp"):
+            e, top, f = g["experts"], g["top"], g["ff"]
+            flops += 2 * tokens * (top * 3 * f * d + e * d)
+            hit = e * (1 - (1 - top / e) ** batch)
+            weights += 2 * (hit * 3 * f * d + e * d)
+    head = 2 * g["vocab"] * d
+    return flops + head, weights + head + cache
+
+
+class GoletarMeasured(Measured):
+    """A Goletar model of given layers on the device, measured like the Llama one."""
+
+    def __init__(self, layers, room, max_prompt, slots):
+        import torch
+
+        from fms_b200.models.goletar import Goletar, GoletarConfig
+        from fms_b200.weights.sources import RandomSource
+
+        g = GOLETAR_SHAPE
+        self.m, self.dtype, self.nlayers, self.itemsize, self.layers = dict(vocab=g["vocab"]), "bf16", len(layers), 2, layers
+        self.model = Goletar(GoletarConfig(vocab=g["vocab"], width=g["width"], layers=layers))
+        self.model.load(RandomSource(self.model.checkpoint_layout(), 0, dtype=torch.bfloat16, device="cuda"), "native", "cuda",
+                        torch.bfloat16)
+        self.engine = self.model.new_engine(max_tokens=slots * (max_prompt + 2 * room + 128), max_slots=slots)
+        self.torch = torch
+
+
+def run_goletar(args):
+    """One JSON line: prompts of 512 and 2,048 tokens and decode steps of 1, 8 and 64 sequences, for `--layers` layers
+    (default 4) of the Goletar design at the width of the benchmark's Llama (alternating minGRU and latent attention,
+    each with 16 experts of 3,584 of which a token takes 4: the dense feed-forward's 14,336 hidden values a token), for as
+    many Llama-3-8B layers, and for each of Goletar's parts alone (models of one kind of layer, with and without
+    experts).  Each figure with its fraction of the measured peak: flops of a prompt over the bf16 product peak, bytes
+    a decode step reads over the copy peak."""
+    pk = peaks()
+    n = args.layers or 4
+    steps, warm = max(16, args.steps // 2), max(3, args.warmup // 2)
+    room = warm + 3 * steps + 8
+    lengths = {1: [1024], 8: [1024] * 8, 64: [1024] * 64}
+    out = {"compare": "goletar", "layers": n, "shape": GOLETAR_SHAPE, "peaks": pk, "steps": steps, "warmup": warm, "models": {}}
+
+    def measure(run, name, flops_bytes):
+        row = {}
+        for tokens in (512, 2048):
+            ms = run.prefill(tokens, 3)
+            row[f"prefill_{tokens}"] = {"ms": round(ms, 3), "tok_s": round(tokens / (ms / 1e3), 1),
+                                        "frac_of_bf16_peak": round(flops_bytes(tokens, 0, 0)[0] / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4)}
+        for b in (1, 8, 64):
+            v, ms, ctx, _, _ = run.device_decode(b, steps, warm, lengths[b], regions=3)
+            row[f"decode_b{b}"] = {"ms": round(ms, 4), "tok_s": round(v, 1),
+                                   "frac_of_copy_peak": round(flops_bytes(0, ctx, b)[1] / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+        out["models"][name] = row
+        run.close()
+
+    kinds = ["mingru" if i % 2 == 0 else "latent_attention" for i in range(n)]
+    variants = [("goletar", goletar_layers(kinds)), ("mingru_only", goletar_layers(["mingru"] * n, False)),
+                ("latent_attention_only", goletar_layers(["latent_attention"] * n, False)),
+                ("mingru_with_experts", goletar_layers(["mingru"] * n))]
+    if args.only:
+        variants = [v for v in variants if v[0] == args.only]
+    for name, layers in variants:
+        measure(GoletarMeasured(layers, room, 2048, 64), name,
+                lambda tokens, ctx, b, layers=layers: goletar_counts(layers, tokens, ctx, b))
+    if not args.only or args.only == "llama":
+        llama = Measured(MODEL, "bf16", n, room, 2048, slots=64)
+        measure(llama, "llama", lambda tokens, ctx, b: (prefill_flops(n, tokens), decode_bytes(n, ctx)))
+    print(json.dumps(out))
+
+
+# --------------------------------------------------------------------------------------------------
 # the reference, unmodified, through its own public API
 # --------------------------------------------------------------------------------------------------
 def run_reference(args):
@@ -562,13 +665,18 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: the prompt's length")
     ap.add_argument("--points", choices=["default", "main", "long"], default="default",
                     help="main: without the further configurations; long: also decode at batch 64 with 8k contexts")
+    ap.add_argument("--compare", choices=["", "goletar"], default="",
+                    help="goletar: the Goletar design beside as many Llama layers of equal width (--layers, default 4; "
+                    "--only goletar|mingru_only|latent_attention_only|mingru_with_experts|llama for one of them)")
     args = ap.parse_args()
     choose_model(args.model)
     if args.gpus != 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not measured")
         sys.exit(2)
-    if args.impl == "reference":
+    if args.compare == "goletar":
+        run_goletar(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.only in ("gemm_rows", "attention_prefill", "attention_decode"):
         run_kernels(args)

@@ -121,33 +121,99 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const T* __restrict__
   }
 }
 
-// Few rows a group (a decode step's pairs): a block per (row, 8 outputs); every warp one output (two with glu), its
-// lanes striding over k.  The group of a row comes from `group_of_row`.  The sums are taken in another order than
-// the tiles' above, so the two differ by rounding.
+// Few rows a group (a decode step): a block per (group, 8 outputs), a warp per output (two with glu), its lanes striding
+// over k; the warp walks the group's rows four at a time, so a group's matrix is read once however many of the step's
+// rows it has (and not at all where it has none).  Ragged groups (offsets) or uniform ones (`rows` rows each, walked
+// by strides as in the tiled kernel).  The sums are taken in another order than the tiles', so the two differ by
+// rounding; a row's own sums do not depend on the other rows.
+__device__ __forceinline__ void rows_load8(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void rows_load8(const __nv_bfloat16* p, float* v) {
+  const uint4 t = *reinterpret_cast<const uint4*>(p);
+  const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    v[2 * k] = __uint_as_float(u[k] << 16);
+    v[2 * k + 1] = __uint_as_float(u[k] & 0xffff0000u);
+  }
+}
+
+// vec != 0: K, the strides and the group offsets are multiples of 8 values and the bases 16-byte aligned: a lane reads 8
+// values at a time
 template <typename T, bool GLU>
-__global__ void __launch_bounds__(256) grouped_gemv_kernel(const T* __restrict__ x, const T* __restrict__ w,
-                                                           T* __restrict__ y, const int* __restrict__ group_of_row,
-                                                           int groups, int N, int K, float limit, float alpha) {
+__global__ void __launch_bounds__(256) grouped_rows_kernel(const T* x, const T* w, T* y, const int* offsets, int groups,
+                                                           int rows, int N, int K, long x_row_stride, long x_group_offset,
+                                                           long y_row_stride, long y_group_offset, float limit,
+                                                           float alpha, int vec) {
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.y;
-  const int g = ld_fresh(group_of_row + r);
-  if (g < 0 || !FMS_IN(g, groups)) return;
+  const int g = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * 8 + warp;
-  if (n >= N) return;
-  const T* xr = x + (size_t)r * K;
+  int r_lo = 0, r_hi = rows;
+  if (offsets != nullptr) {
+    r_lo = ld_fresh(offsets + g);
+    r_hi = ld_fresh(offsets + g + 1);
+  } else {
+    x += (size_t)g * x_group_offset;
+    y += (size_t)g * y_group_offset;
+  }
+  if (n >= N || r_lo >= r_hi) return;
   const T* w0 = w + ((size_t)g * (GLU ? 2 : 1) * N + n) * K;
   const T* w1 = w0 + (size_t)N * K;
-  float a0 = 0.f, a1 = 0.f;
-  for (int k = lane; k < K; k += 32) {
-    const float xv = to_f32(xr[k]);
-    a0 = fmaf(xv, to_f32(w0[k]), a0);
-    if (GLU) a1 = fmaf(xv, to_f32(w1[k]), a1);
+  for (int r0 = r_lo; r0 < r_hi; r0 += 4) {
+    const int nr = min(4, r_hi - r0);
+    float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec) {
+      for (int k = lane * 8; k < K; k += 256) {
+        float wa[8], wb[8];
+        rows_load8(w0 + k, wa);
+        if (GLU) rows_load8(w1 + k, wb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (i < nr) {
+            float xv[8];
+            rows_load8(x + (size_t)(r0 + i) * x_row_stride + k, xv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              a0[i] = fmaf(xv[e], wa[e], a0[i]);
+              if (GLU) a1[i] = fmaf(xv[e], wb[e], a1[i]);
+            }
+          }
+      }
+    } else
+    for (int k = lane; k < K; k += 32) {
+      const float wa = to_f32(w0[k]), wb = GLU ? to_f32(w1[k]) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (i < nr) {
+          const float xv = to_f32(x[(size_t)(r0 + i) * x_row_stride + k]);
+          a0[i] = fmaf(xv, wa, a0[i]);
+          if (GLU) a1[i] = fmaf(xv, wb, a1[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (i < nr) {
+        const float s0 = warp_sum(a0[i]), s1 = GLU ? warp_sum(a1[i]) : 0.f;
+        if (lane == 0) y[(size_t)(r0 + i) * y_row_stride + n] = from_f32<T>(GLU ? glu_clamped(s0, s1, limit, alpha) : s0);
+      }
   }
-  a0 = warp_sum(a0);
-  if (GLU) a1 = warp_sum(a1);
-  if (lane == 0) y[(size_t)r * N + n] = from_f32<T>(GLU ? glu_clamped(a0, a1, limit, alpha) : a0);
+}
+
+// The gated unit alone, for rows [gate | up] that a library product left: out[r, f] = act(gate) * (up + 1), clamped
+// as above.
+template <typename T>
+__global__ void gated_clamped_kernel(const T* gu, T* out, int hidden, float limit, float alpha, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / hidden;
+    const int f = (int)(i - r * hidden);
+    out[i] = from_f32<T>(glu_clamped(to_f32(gu[r * 2 * hidden + f]), to_f32(gu[r * 2 * hidden + hidden + f]), limit, alpha));
+  }
 }
 
 // ---- routing -----------------------------------------------------------------------------------------
@@ -278,8 +344,7 @@ __global__ void __launch_bounds__(128) route_gather_kernel(const T* __restrict__
 FMS_API int fms_grouped_tile_rows() { return BM; }
 
 // offsets null: uniform groups of `rows` rows; else ragged groups, `rows` = all rows of x, and tile_first as
-// fms_route leaves it.  few_rows != 0 (ragged, contiguous rows of K and N values): the row-by-row kernel, which reads
-// each row's group from group_of_row.
+// fms_route leaves it.  few_rows != 0: the kernel that walks each group's rows (a decode step).
 FMS_API int fms_grouped_linear(const void* x, const void* w, void* y, int dtype, const int* offsets, const int* tile_first,
                                const int* group_of_row, int groups, int rows, int N, int K, long x_row_stride,
                                long x_group_offset, long y_row_stride, long y_group_offset, int glu, float limit,
@@ -287,17 +352,17 @@ FMS_API int fms_grouped_linear(const void* x, const void* w, void* y, int dtype,
   if (rows <= 0 || groups <= 0 || N <= 0) return 0;
   if (K <= 0) return fms_fail("grouped_linear: K %d", K);
   if (few_rows) {
-    if (group_of_row == nullptr || x_row_stride != K || y_row_stride != N)
-      return fms_fail("grouped_linear: the row-by-row kernel takes contiguous rows and a group for each");
-    if (rows > 65535) return fms_fail("grouped_linear: %d rows are more than the row-by-row kernel takes", rows);
-    dim3 grid((N + 7) / 8, rows);
+    if (groups > 65535) return fms_fail("grouped_linear: %d groups are more than the row-by-row kernel takes", groups);
+    dim3 grid((N + 7) / 8, groups);
+    const int vec = K % 8 == 0 && x_row_stride % 8 == 0 && x_group_offset % 8 == 0 && ((uintptr_t)x & 15) == 0 &&
+                    ((uintptr_t)w & 15) == 0;
     FMS_DISPATCH_DTYPE(dtype, T, {
       if (glu)
-        fms_launch(grouped_gemv_kernel<T, true>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y, group_of_row,
-                   groups, N, K, limit, alpha);
+        fms_launch(grouped_rows_kernel<T, true>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y, offsets, groups,
+                   rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha, vec);
       else
-        fms_launch(grouped_gemv_kernel<T, false>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y,
-                   group_of_row, groups, N, K, limit, alpha);
+        fms_launch(grouped_rows_kernel<T, false>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y, offsets, groups,
+                   rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha, vec);
     });
     return fms_launch_status("grouped_linear (few rows)");
   }
@@ -346,6 +411,17 @@ FMS_API int fms_route(const void* x, int dtype, const void* router, int router_d
                                 (const float*)weight, (const int*)offsets, counts, row_of_pair, group_of_row, (T*)xs, dim,
                                 top, experts, n_pairs));
   return fms_launch_status("route (scatter)");
+}
+
+FMS_API int fms_gated_clamped(const void* gu, void* out, int dtype, int n_rows, int hidden, float limit, float alpha,
+                              cudaStream_t stream) {
+  if (n_rows <= 0 || hidden <= 0) return 0;
+  const size_t total = (size_t)n_rows * hidden;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  FMS_DISPATCH_DTYPE(dtype, T,
+                     fms_launch(gated_clamped_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)gu, (T*)out, hidden,
+                                limit, alpha, total));
+  return fms_launch_status("gated_clamped");
 }
 
 FMS_API int fms_route_gather(const void* ys, int dtype, const int* row_of_pair, void* out, int n_tokens, int dim, int top,

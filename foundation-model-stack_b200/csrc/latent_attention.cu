@@ -149,13 +149,14 @@ __global__ void __launch_bounds__(THREADS) latent_attention_kernel(LatentArgs a)
   for (int k0 = lo; k0 < hi; k0 += KT) {
     __syncthreads();  // the last tile's sums are taken (and, the first time, q is in place)
     const int nk = min(KT, hi - k0);
-    for (int i = threadIdx.x; i < nk * width; i += THREADS) {
-      const int j = i / width, d = i - j * width;
-      const int p = k0 + j;
-      const int blk = a.table[(size_t)slot * a.table_stride + p / a.block_tokens];
-      float v = 0.f;
-      if (blk >= 0 && blk < a.n_blocks) v = to_f32(cache[((size_t)blk * a.block_tokens + p % a.block_tokens) * width + d]);
-      ks[j * kstride + d] = v;
+    {
+      // a tile of KT keys lies inside one cache block (KT divides the block's tokens): one look at the table; a warp
+      // brings whole rows, its lanes striding over a row
+      const int blk = a.table[(size_t)slot * a.table_stride + k0 / a.block_tokens];
+      const bool held = blk >= 0 && blk < a.n_blocks;
+      const T* src = cache + ((size_t)(held ? blk : 0) * a.block_tokens + k0 % a.block_tokens) * width;
+      for (int j = warp; j < nk; j += THREADS / 32)
+        for (int d = lane; d < width; d += 32) ks[j * kstride + d] = held ? to_f32(src[(size_t)j * width + d]) : 0.f;
     }
     __syncthreads();
     if (warp < nh) {
@@ -163,9 +164,16 @@ __global__ void __launch_bounds__(THREADS) latent_attention_kernel(LatentArgs a)
       if (lane < nk) {
         const float* qh = qs + warp * width;
         const float* kj = ks + lane * kstride;
-        float dot = 0.f;
-        for (int d = 0; d < width; ++d) dot = fmaf(qh[d], kj[d], dot);
-        s = dot * a.scale;
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;  // four chains: none waits for the one before
+        int d = 0;
+        for (; d + 3 < width; d += 4) {
+          d0 = fmaf(qh[d], kj[d], d0);
+          d1 = fmaf(qh[d + 1], kj[d + 1], d1);
+          d2 = fmaf(qh[d + 2], kj[d + 2], d2);
+          d3 = fmaf(qh[d + 3], kj[d + 3], d3);
+        }
+        for (; d < width; ++d) d0 = fmaf(qh[d], kj[d], d0);
+        s = ((d0 + d1) + (d2 + d3)) * a.scale;
       }
       const float m_new = fmaxf(m_run, warp_max(s));
       const float p = lane < nk ? expf(s - m_new) : 0.f;
@@ -182,13 +190,13 @@ __global__ void __launch_bounds__(THREADS) latent_attention_kernel(LatentArgs a)
         const float al = alpha[h];
         const float* ph = ps + h * KT;
 #pragma unroll
-        for (int i = 0; i < NACC; ++i) {
-          const int d = lane + 32 * i;
-          if (d < a.rank) {
-            float v = acc[i] * al;
-            for (int j = 0; j < nk; ++j) v = fmaf(ph[j], ks[j * kstride + d], v);
-            acc[i] = v;
-          }
+        for (int i = 0; i < NACC; ++i) acc[i] *= al;
+        for (int j = 0; j < nk; ++j) {
+          const float pj = ph[j];
+          const float* cj = ks + j * kstride + lane;
+#pragma unroll
+          for (int i = 0; i < NACC; ++i)
+            if (lane + 32 * i < a.rank) acc[i] = fmaf(pj, cj[32 * i], acc[i]);
         }
       }
     }
@@ -248,11 +256,208 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(LatentArgs a) {
   }
 }
 
+// ---- many rows, bfloat16: the two products on the tensor cores (mma.sync m16n8k16, float32 sums) ---------------
+// A block owns MR = 32 rows: `tq` consecutive tokens of one sequence times `hb` heads (tq * hb = 32), all of which
+// read the same keys.  Keys come MK = 32 at a time into shared memory (cp.async, two stages; keys beyond the
+// tile's last position are zeros).  Per tile: (A) warp w takes the scores of 16 rows against 8 keys over the whole
+// row width; (B) eight threads a row take the running maximum, the probabilities (bfloat16, as in every
+// flash-attention kernel) and the sum; (C) warp w adds P . c for 16 rows and a quarter of the latent's columns
+// (rank / 4, its share of the accumulator in registers), c being read as it lies in the key tile.
+constexpr int MR = 32, MK = 32;
+
+__device__ __forceinline__ void lat_mma(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void lat_ldmatrix(uint32_t* r, const void* row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(row)));
+}
+__device__ __forceinline__ void lat_ldmatrix_trans(uint32_t* r, const void* row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(row)));
+}
+__device__ __forceinline__ void lat_copy16(void* smem, const void* gmem, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes) : "memory");
+}
+
+template <typename TS, int NT>
+__global__ void __launch_bounds__(256) latent_prefill_mma_kernel(LatentArgs a, const int* tiles, const int* first_row,
+                                                                 int tq, int hb) {
+  extern __shared__ __align__(16) unsigned char lat_smem[];
+  const int width = a.rank + a.rot;
+  const int rowb = width * 2 + 16, prowb = MK * 2 + 16;
+  unsigned char* qs = lat_smem;
+  unsigned char* ks = qs + MR * rowb;
+  float* ss = reinterpret_cast<float*>(ks + 2 * MK * rowb);
+  unsigned char* ps = reinterpret_cast<unsigned char*>(ss + MR * (MK + 1));
+  float* m_s = reinterpret_cast<float*>(ps + MR * prowb);
+  float* l_s = m_s + MR;
+  float* al_s = l_s + MR;
+  int* pos_s = reinterpret_cast<int*>(al_s + MR);
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int seq = tiles[2 * blockIdx.x], r0 = tiles[2 * blockIdx.x + 1], h0 = blockIdx.y * hb;
+  if (!FMS_IN(seq, a.n_seqs)) return;
+  const int slot = a.slots[seq];
+  if (!FMS_IN(slot, a.n_slots)) return;
+  const int first = first_row[seq] + r0;
+  const int ntok = min(tq, first_row[seq + 1] - first);
+  if (ntok <= 0) return;
+  const int last_pos = ld_fresh(a.positions + first + ntok - 1);
+  if (tid < MR) {
+    const int tok = tid / hb, hh = tid - tok * hb;
+    pos_s[tid] = (tok < ntok && h0 + hh < a.heads) ? ld_fresh(a.positions + first + tok) : -1;
+    m_s[tid] = -INFINITY;
+    l_s[tid] = 0.f;
+  }
+  const __nv_bfloat16* q = (const __nv_bfloat16*)a.q;
+  const __nv_bfloat16* cache = (const __nv_bfloat16*)a.cache;
+  const int pieces = width / 8;
+  for (int i = tid; i < MR * pieces; i += 256) {
+    const int r = i / pieces, piece = i - r * pieces;
+    const int tok = r / hb, hh = r - tok * hb;
+    const bool ok = tok < ntok && h0 + hh < a.heads;
+    lat_copy16(qs + r * rowb + piece * 16, q + ((size_t)(first + (ok ? tok : 0)) * a.heads + (ok ? h0 + hh : 0)) * width + piece * 8, ok);
+  }
+  auto load_keys = [&](int kt) {
+    unsigned char* dst = ks + (kt & 1) * MK * rowb;
+    for (int i = tid; i < MK * pieces; i += 256) {
+      const int j = i / pieces, piece = i - j * pieces;
+      const int p = kt * MK + j;
+      int blk = -1;
+      if (p <= last_pos) blk = a.table[(size_t)slot * a.table_stride + p / a.block_tokens];
+      const bool ok = blk >= 0 && blk < a.n_blocks;
+      lat_copy16(dst + j * rowb + piece * 16, cache + ((size_t)(ok ? blk : 0) * a.block_tokens + p % a.block_tokens) * width + piece * 8, ok);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  load_keys(0);  // one group: the queries and the first keys
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const int rg = warp & 1, part = warp >> 1;
+  const int n_kt = last_pos / MK + 1;
+  for (int kt = 0; kt < n_kt; ++kt) {
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();  // tile kt is in place for everyone, and everyone is done with the other stage
+    if (kt + 1 < n_kt) load_keys(kt + 1);
+    const unsigned char* kst = ks + (kt & 1) * MK * rowb;
+    {  // (A) scores of rows rg * 16 .. + 15 against keys part * 8 .. + 7
+      float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+      const unsigned char* qrow = qs + (rg * 16 + (lane & 15)) * rowb + (lane >> 4) * 16;
+      const unsigned char* krow = kst + (part * 8 + (lane & 7)) * rowb + (lane >> 3) * 16;
+      for (int kk = 0; kk < width / 32; ++kk) {
+        uint32_t a0[4], a1[4], b[4];
+        lat_ldmatrix(a0, qrow + kk * 64);
+        lat_ldmatrix(a1, qrow + kk * 64 + 32);
+        lat_ldmatrix(b, krow + kk * 64);
+        lat_mma(sacc, a0, b[0], b[1]);
+        lat_mma(sacc, a1, b[2], b[3]);
+      }
+      float* dst = ss + (rg * 16 + (lane >> 2)) * (MK + 1) + part * 8 + 2 * (lane & 3);
+      dst[0] = sacc[0];
+      dst[1] = sacc[1];
+      dst[8 * (MK + 1)] = sacc[2];
+      dst[8 * (MK + 1) + 1] = sacc[3];
+    }
+    __syncthreads();
+    {  // (B) eight threads a row, four keys each
+      const int r = tid >> 3, sub = tid & 7;
+      const int pos = pos_s[r];
+      const float m_old = m_s[r];
+      float sv[4], mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = kt * MK + sub * 4 + j;
+        sv[j] = key <= pos ? ss[r * (MK + 1) + sub * 4 + j] * a.scale : -INFINITY;
+        mx = fmaxf(mx, sv[j]);
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_new = fmaxf(m_old, mx);
+      float pv[4], sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        pv[j] = m_new == -INFINITY ? 0.f : expf(sv[j] - m_new);
+        sum += pv[j];
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      __nv_bfloat162* pd = reinterpret_cast<__nv_bfloat162*>(ps + r * prowb + sub * 8);
+      pd[0] = __floats2bfloat162_rn(pv[0], pv[1]);
+      pd[1] = __floats2bfloat162_rn(pv[2], pv[3]);
+      if (sub == 0) {
+        const float al = m_new == -INFINITY ? 1.f : expf(m_old - m_new);
+        m_s[r] = m_new;
+        l_s[r] = l_s[r] * al + sum;
+        al_s[r] = al;
+      }
+    }
+    __syncthreads();
+    {  // (C) rows rg * 16 .. + 15, columns part * rank / 4 .. of the latent
+      const float al0 = al_s[rg * 16 + (lane >> 2)], al1 = al_s[rg * 16 + (lane >> 2) + 8];
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        acc[i][0] *= al0; acc[i][1] *= al0; acc[i][2] *= al1; acc[i][3] *= al1;
+      }
+      const int c0 = part * NT * 8;
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        uint32_t pa[4];
+        lat_ldmatrix(pa, ps + (rg * 16 + (lane & 15)) * prowb + kk * 32 + (lane >> 4) * 16);
+        const unsigned char* vrow = kst + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * rowb + (c0 + (lane >> 4) * 8) * 2;
+#pragma unroll
+        for (int i = 0; i < NT / 2; ++i) {
+          uint32_t b[4];
+          lat_ldmatrix_trans(b, vrow + i * 32);
+          lat_mma(acc[2 * i], pa, b[0], b[1]);
+          lat_mma(acc[2 * i + 1], pa, b[2], b[3]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < MR) {  // what each row's sums are multiplied by: the softmax's denominator with the sink, and the gate
+    float f = 0.f;
+    if (pos_s[tid] >= 0) {
+      const int tok = tid / hb, h = h0 + tid - tok * hb;
+      float m = m_s[tid], denom = l_s[tid], top = m;
+      if (a.sink) {
+        const float sk = to_f32(((const TS*)a.sink)[h]);
+        top = fmaxf(m, sk);
+        denom = denom * expf(m - top) + expf(sk - top);
+      }
+      f = expf(m - top) / denom;
+      if (a.gate) f *= 1.f / (1.f + expf(-to_f32(((const __nv_bfloat16*)a.gate)[(size_t)(first + tok) * a.gate_stride + h])));
+    }
+    al_s[tid] = f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = rg * 16 + (lane >> 2) + 8 * half;
+    if (pos_s[r] < 0) continue;
+    const int tok = r / hb, h = h0 + r - tok * hb;
+    const float f = al_s[r];
+    __nv_bfloat16* o = (__nv_bfloat16*)a.out + ((size_t)(first + tok) * a.heads + h) * a.rank + part * NT * 8 + 2 * (lane & 3);
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+      *reinterpret_cast<__nv_bfloat162*>(o + i * 8) = __floats2bfloat162_rn(acc[i][2 * half] * f, acc[i][2 * half + 1] * f);
+  }
+}
+
 template <typename T, typename TS>
 int launch_attention(const LatentArgs& a, int n_tokens, cudaStream_t stream) {
   const int width = a.rank + a.rot;
   const size_t smem = ((size_t)HG * width + (size_t)KT * (width | 1) + HG * KT + HG) * sizeof(float);
   if (smem > 220 * 1024) return fms_fail("latent_attention: rows of %d values do not fit shared memory", width);
+  if (a.block_tokens % KT) return fms_fail("latent_attention: cache blocks of %d tokens", a.block_tokens);
   dim3 grid(n_tokens, a.n_splits, (a.heads + HG - 1) / HG);
   if (grid.y > 65535 || grid.z > 65535) return fms_fail("latent_attention: %d splits, %d heads", a.n_splits, a.heads);
 #define FMS_LATENT_LAUNCH(NACC)                                                                                         \
@@ -311,4 +516,47 @@ FMS_API int fms_latent_attention(const void* q, void* out, int dtype, const void
   a.n_splits = n_splits; a.n_seqs = n_seqs; a.n_slots = n_slots; a.n_blocks = n_blocks; a.scale = scale;
   FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(sink ? sink_dtype : dtype, TS, return launch_attention<T, TS>(a, n_tokens, stream)));
   return 0;
+}
+
+// Many rows of bfloat16 on the tensor cores: rank a multiple of 64 up to 512, rank + rot a multiple of 32.  tiles
+// [n_tiles, 2] = (sequence, first of its `tile_tokens` rows within the sequence's rows of this step); a block takes
+// tile_tokens tokens times heads_per_block heads, tile_tokens * heads_per_block = 32.
+FMS_API int fms_latent_attention_prefill_bf16(const void* q, void* out, const void* cache, const void* gate, long gate_stride,
+                                              const void* sink, int sink_dtype, const int* table, int table_stride,
+                                              int block_tokens, const int* slots, const int* first_row,
+                                              const int* positions, const int* tiles, int n_tiles, int tile_tokens,
+                                              int heads_per_block, int heads, int rank, int rot, float scale, int n_seqs,
+                                              int n_slots, int n_blocks, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  const int width = rank + rot;
+  if (rank % 64 || rank > 512 || width % 32 || tile_tokens * heads_per_block != MR)
+    return fms_fail("latent_attention_prefill: rank %d, rot %d, %d tokens x %d heads a block", rank, rot, tile_tokens, heads_per_block);
+  LatentArgs a;
+  a.q = q; a.out = out; a.cache = cache; a.gate = gate; a.sink = sink; a.table = table; a.slots = slots;
+  a.token_seq = nullptr; a.positions = positions; a.part_o = nullptr; a.part_ml = nullptr; a.gate_stride = gate_stride;
+  a.table_stride = table_stride; a.block_tokens = block_tokens; a.heads = heads; a.rank = rank; a.rot = rot;
+  a.n_splits = 1; a.n_seqs = n_seqs; a.n_slots = n_slots; a.n_blocks = n_blocks; a.scale = scale;
+  const int rowb = width * 2 + 16;
+  const size_t smem = (size_t)(MR + 2 * MK) * rowb + MR * (MK + 1) * 4 + MR * (MK * 2 + 16) + MR * 16;
+  dim3 grid(n_tiles, (heads + heads_per_block - 1) / heads_per_block);
+#define FMS_LATENT_MMA(NT)                                                                                              \
+  case NT:                                                                                                              \
+    if (sink && sink_dtype == FMS_F32) {                                                                                \
+      cudaFuncSetAttribute(latent_prefill_mma_kernel<float, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      fms_launch(latent_prefill_mma_kernel<float, NT>, grid, dim3(256), smem, stream, a, tiles, first_row, tile_tokens,   \
+                 heads_per_block);                                                                                      \
+    } else {                                                                                                            \
+      cudaFuncSetAttribute(latent_prefill_mma_kernel<__nv_bfloat16, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                           (int)smem);                                                                                  \
+      fms_launch(latent_prefill_mma_kernel<__nv_bfloat16, NT>, grid, dim3(256), smem, stream, a, tiles, first_row,       \
+                 tile_tokens, heads_per_block);                                                                         \
+    }                                                                                                                   \
+    break;
+  switch (rank / 32) {
+    FMS_LATENT_MMA(2) FMS_LATENT_MMA(4) FMS_LATENT_MMA(6) FMS_LATENT_MMA(8) FMS_LATENT_MMA(10) FMS_LATENT_MMA(12)
+    FMS_LATENT_MMA(14) FMS_LATENT_MMA(16)
+    default: return fms_fail("latent_attention_prefill: rank %d", rank);
+  }
+#undef FMS_LATENT_MMA
+  return fms_launch_status("latent_attention_prefill");
 }

@@ -58,6 +58,9 @@ _SIGNATURES = {
     "fms_grouped_linear": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _I, _F, _F, _I, _P],
     "fms_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fms_route_gather": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "fms_gated_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
+    "fms_latent_attention_prefill_bf16": [_P, _P, _P, _P, _L, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                                          _F, _I, _I, _I, _P],
     "fms_latent_prepare": [_P, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
                            _I, _I, _P, _P],
     "fms_latent_attention": [_P, _P, _I, _P, _P, _L, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I,
@@ -563,7 +566,9 @@ def mingru_scan(proj: torch.Tensor, state: torch.Tensor, batch, width: int, writ
 
 
 # ---- groups of rows, each with a matrix of its own ---------------------------------------------------
-GROUPED_FEW_ROWS = 32  # rows up to which the ragged product goes row by row
+GROUPED_FEW_ROWS = 32  # rows of a step up to which the grouped products walk each group's rows (a decode step)
+# FMS_B200_GROUPED_LIBRARY=0: the own float32-sum kernel for the ragged products of many bfloat16 rows too
+USE_LIBRARY_GROUPED = os.environ.get("FMS_B200_GROUPED_LIBRARY", "1") != "0" and hasattr(torch.nn.functional, "grouped_mm")
 
 
 def grouped_linear(x: torch.Tensor, weight: torch.Tensor, groups: int, rows: int, n_out: int, k: int, x_row_stride: int,
@@ -572,8 +577,16 @@ def grouped_linear(x: torch.Tensor, weight: torch.Tensor, groups: int, rows: int
     for r < rows (x and y are walked by their row strides; weight [groups, n_out, k])."""
     if weight.dtype != x.dtype or y.dtype != x.dtype or tuple(weight.shape) != (groups, n_out, k):
         raise KernelError(f"grouped_linear: x {x.dtype}, weight {weight.dtype} {tuple(weight.shape)}, y {y.dtype}")
+    _ptr(x), _ptr(weight), _ptr(y)
+    if USE_LIBRARY_GROUPED and x.dtype == torch.bfloat16 and rows > GROUPED_FEW_ROWS:
+        # many bfloat16 rows: the library's batched product over strided views of x and y (no copy of either)
+        xv = torch.as_strided(x, (groups, rows, k), (x_group_offset, x_row_stride, 1), x.storage_offset())
+        yv = torch.as_strided(y, (groups, rows, n_out), (y_group_offset, y_row_stride, 1), y.storage_offset())
+        torch.bmm(xv, weight.transpose(1, 2), out=yv)
+        return y
     _call("grouped", "fms_grouped_linear", _ptr(x), _ptr(weight), _ptr(y), _code(x.dtype), None, None, None, groups, rows,
-          n_out, k, x_row_stride, x_group_offset, y_row_stride, y_group_offset, 0, 0.0, 0.0, 0, _stream())
+          n_out, k, x_row_stride, x_group_offset, y_row_stride, y_group_offset, 0, 0.0, 0.0,
+          1 if rows <= GROUPED_FEW_ROWS else 0, _stream())
     return y
 
 
@@ -618,6 +631,18 @@ def routed_linear(rows: torch.Tensor, weight: torch.Tensor, routing: Routing, gl
     n_out = weight.shape[1] // (2 if glu else 1)
     if weight.dtype != rows.dtype or weight.shape[0] != routing.experts or weight.shape[2] != k:
         raise KernelError(f"routed_linear: rows {rows.dtype} {tuple(rows.shape)}, weight {weight.dtype} {tuple(weight.shape)}")
+    if (USE_LIBRARY_GROUPED and rows.dtype == torch.bfloat16 and n > GROUPED_FEW_ROWS and k % 8 == 0
+            and weight.shape[1] % 8 == 0):
+        # many bfloat16 rows: the library's grouped product (it takes the groups' ends from the device, as the
+        # own kernels do), as the plain products of many rows take the library's; the gated unit is a kernel after it
+        _ptr(rows), _ptr(weight)
+        y = torch.nn.functional.grouped_mm(rows, weight.transpose(1, 2), offs=routing.offsets[1:])
+        if not glu:
+            return y
+        out = torch.empty((n, n_out), dtype=rows.dtype, device=rows.device)
+        _call("grouped", "fms_gated_clamped", _ptr(y), _ptr(out), _code(y.dtype), n, n_out, float(limit), float(alpha),
+              _stream())
+        return out
     y = torch.empty((n, n_out), dtype=rows.dtype, device=rows.device)
     _call("grouped", "fms_grouped_linear", _ptr(rows), _ptr(weight), _ptr(y), _code(rows.dtype), _ptr(routing.offsets),
           _ptr(routing.tile_first), _ptr(routing.group_of_row), routing.experts, n, n_out, k, k, 0, n_out, 0,
@@ -636,6 +661,7 @@ def route_gather(ys: torch.Tensor, routing: Routing) -> torch.Tensor:
 
 # ---- attention over cached latents -------------------------------------------------------------------
 _latent_split = None
+USE_LATENT_MMA = os.environ.get("FMS_B200_LATENT_MMA", "1") != "0"  # 0: a prompt's rows through the float32 kernel too
 
 
 def latent_prepare(proj: torch.Tensor, q_full: torch.Tensor, c_gain: torch.Tensor, eps: float, inv_freq: torch.Tensor,
@@ -661,6 +687,21 @@ def latent_attention(q_full: torch.Tensor, batch, view, gate: Optional[torch.Ten
     global _latent_split
     n = q_full.shape[0]
     out = torch.empty((n, heads, rank), dtype=q_full.dtype, device=q_full.device)
+    if (USE_LATENT_MMA and not batch.decode and q_full.dtype == torch.bfloat16 and rank % 64 == 0 and rank <= 512
+            and (rank + rot) % 32 == 0 and (gate is None or gate.dtype == torch.bfloat16)):
+        # a prompt's rows: both products on the tensor cores, 32 rows (tokens x heads) a block
+        heads_per_block = 1
+        while heads_per_block < min(32, heads):
+            heads_per_block *= 2
+        tile_tokens = 32 // heads_per_block
+        tiles = batch.query_tiles(tile_tokens)
+        gate_ptr = None if gate is None else _ptr(gate) + gate_offset * gate.element_size()
+        _call("latent_attention", "fms_latent_attention_prefill_bf16", _ptr(q_full), _ptr(out), _ptr(view.keys), gate_ptr,
+              0 if gate is None else gate.shape[1], _ptr(sink), _code(sink.dtype) if sink is not None else F32,
+              _ptr(view.table), view.table.shape[1], view.block_tokens, _ptr(batch.slots), _ptr(batch.first_row),
+              _ptr(batch.positions), _ptr(tiles), tiles.shape[0], tile_tokens, heads_per_block, heads, rank, rot,
+              float(scale), batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())
+        return out
     n_splits, part_o, part_ml = 1, None, None
     if batch.decode:
         if _latent_split is None:

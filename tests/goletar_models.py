@@ -41,6 +41,11 @@ CONFIGS = {
                           latent(1, 8, 24, 40, 32, 100.0, experts(7, 3, 12, 2.5)),
                           latent(5, 24, 4, 8, 16, 100.0, None)], eps=1e-6, buckets=257, mul_prev=40_000_003,
                 mul_cur=1_000_033),
+    # a latent of 64 values and a row of 96: a prompt's rows of this one take the tensor-core attention kernel in
+    # bfloat16 (five heads: a block holds four tokens of eight head places, three of them empty), and its experts'
+    # products the library's grouped product
+    "s": config(101, 64, [latent(5, 16, 32, 24, 64, 1000.0, experts(6, 2, 24, 1.0)), mingru(48, experts(6, 2, 24, 1.0)),
+                          latent(5, 16, 32, 24, 64, 1000.0, None)], eps=1e-5, buckets=53, mul_prev=11, mul_cur=3),
     # sizes that are no multiples of 8 or 32, nine heads (more than one block of the attention kernel takes)
     "r": config(75, 36, [latent(9, 6, 2, 5, 10, 20.0, experts(4, 4, 9, 1.5)), mingru(35, experts(4, 4, 9, 1.5))],
                 eps=1e-5, buckets=11, mul_prev=1, mul_cur=1),

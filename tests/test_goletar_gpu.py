@@ -186,7 +186,8 @@ def latent_mixer(m, dim_in, w, eps, dt):
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("shape", [(3, 16, 8, 12, 24, 8), (9, 6, 2, 5, 10, 2), (2, 32, 16, 64, 130, 6), (1, 0, 8, 8, 8, 8)])
+@pytest.mark.parametrize("shape", [(3, 16, 8, 12, 24, 8), (9, 6, 2, 5, 10, 2), (2, 32, 16, 64, 130, 6), (1, 0, 8, 8, 8, 8),
+                                   (5, 16, 32, 24, 64, 32), (33, 8, 64, 16, 192, 10), (2, 24, 0, 8, 128, 0)])
 def test_latent_attention_alone(dtype, shape):
     heads, dim, rot, vdim, rank, dims = shape
     m = gm.latent(heads, dim, rot, vdim, rank, 300.0, None, rot_dims=dims)["mixer"]
@@ -223,7 +224,7 @@ def test_latent_attention_sink_and_a_far_key():
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("n_experts,top,rows", [(5, 1, 70), (5, 2, 3), (8, 3, 200), (4, 4, 33), (16, 2, 1)])
+@pytest.mark.parametrize("n_experts,top,rows", [(5, 1, 70), (5, 2, 3), (8, 3, 200), (4, 4, 33), (16, 2, 1), (6, 2, 700)])
 def test_routed_experts_alone(dtype, n_experts, top, rows):
     from fms_b200.config import FeedForwardSpec
     from fms_b200.parts import build_feed_forward
@@ -282,7 +283,7 @@ def test_pair_hash_embedding_alone():
 
 # ---- whole models -------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("which", ["p", "q", "r"])
+@pytest.mark.parametrize("which", ["p", "q", "r", "s"])
 def test_whole_prompts_alone(folders, oracles, which, dtype):
     model = model_of(folders, which, dtype)
     engine = model.new_engine(max_tokens=1024, sampling=False)
@@ -328,7 +329,7 @@ def test_prompt_then_long_decoding_over_split_edges(folders, oracles, which, dty
     engine.check()
 
 
-@pytest.mark.parametrize("which,dtype", [("p", "fp32"), ("q", "fp32"), ("r", "fp32"), ("p", "bf16")])
+@pytest.mark.parametrize("which,dtype", [("p", "fp32"), ("q", "fp32"), ("r", "fp32"), ("p", "bf16"), ("s", "bf16")])
 def test_prompts_cut_into_portions(folders, oracles, which, dtype):
     engine = model_of(folders, which, dtype).new_engine(max_tokens=1024, sampling=False)
     ids = gm.prompt(gm.CONFIGS[which], 420, 41)
@@ -345,7 +346,7 @@ def test_prompts_cut_into_portions(folders, oracles, which, dtype):
     engine.check()
 
 
-@pytest.mark.parametrize("which,dtype", [("p", "fp32"), ("q", "fp32"), ("r", "fp32"), ("q", "bf16")])
+@pytest.mark.parametrize("which,dtype", [("p", "fp32"), ("q", "fp32"), ("r", "fp32"), ("q", "bf16"), ("s", "bf16")])
 def test_unequal_batches_freed_slots_and_poisoned_blocks(folders, oracles, which, dtype):
     """Requests of unequal lengths start together and go on one token at a time while the shorter ones end; then
     everything the cache holds is filled with NaN (keys, states) or junk (the last tokens) and new requests take the
