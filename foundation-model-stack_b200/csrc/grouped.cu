@@ -216,10 +216,35 @@ __global__ void gated_clamped_kernel(const T* gu, T* out, int hidden, float limi
   }
 }
 
+__global__ void gated_clamped_vec_kernel(const __nv_bfloat16* gu, __nv_bfloat16* out, int hidden, float limit, float alpha,
+                                         int n_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = hidden >> 3;
+  const long total = (long)n_rows * per_row;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / per_row;
+    const int f = (int)(i - r * per_row) * 8;
+    float g[8], u[8];
+    rows_load8(gu + r * 2 * hidden + f, g);
+    rows_load8(gu + r * 2 * hidden + hidden + f, u);
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      __nv_bfloat162 v = __floats2bfloat162_rn(glu_clamped(g[2 * k], u[2 * k], limit, alpha),
+                                               glu_clamped(g[2 * k + 1], u[2 * k + 1], limit, alpha));
+      o[k] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    *reinterpret_cast<uint4*>(out + r * hidden + f) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // ---- routing -----------------------------------------------------------------------------------------
 // One block per token.  logits in shared memory; warp 0 then takes the `top` largest one after the other.
+constexpr int ROUTE_WARPS = 8;
+
 template <typename T, typename TW>
-__global__ void __launch_bounds__(128) route_kernel(const T* __restrict__ x, const TW* __restrict__ router,
+__global__ void __launch_bounds__(32 * ROUTE_WARPS) route_kernel(const T* __restrict__ x, const TW* __restrict__ router,
                                                     int* __restrict__ expert, float* __restrict__ weight,
                                                     int dim, int experts, int top) {
   extern __shared__ float sm[];  // dim values of x, then `experts` logits
@@ -230,11 +255,18 @@ __global__ void __launch_bounds__(128) route_kernel(const T* __restrict__ x, con
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int d = threadIdx.x; d < dim; d += blockDim.x) xs[d] = to_f32(x[(size_t)t * dim + d]);
   __syncthreads();
-  for (int e = warp; e < experts; e += 4) {
+  for (int e = warp; e < experts; e += ROUTE_WARPS) {
     const TW* wr = router + (size_t)e * dim;
-    float a = 0.f;
-    for (int d = lane; d < dim; d += 32) a = fmaf(xs[d], to_f32(wr[d]), a);
-    a = warp_sum(a);
+    float a = 0.f, b = 0.f, c = 0.f, d4 = 0.f;  // four chains: the loads of one do not wait for another's sum
+    int d = lane;
+    for (; d + 96 < dim; d += 128) {
+      a = fmaf(xs[d], to_f32(wr[d]), a);
+      b = fmaf(xs[d + 32], to_f32(wr[d + 32]), b);
+      c = fmaf(xs[d + 64], to_f32(wr[d + 64]), c);
+      d4 = fmaf(xs[d + 96], to_f32(wr[d + 96]), d4);
+    }
+    for (; d < dim; d += 32) a = fmaf(xs[d], to_f32(wr[d]), a);
+    a = warp_sum((a + b) + (c + d4));
     if (lane == 0) logit[e] = a;
   }
   __syncthreads();
@@ -325,15 +357,18 @@ __global__ void __launch_bounds__(128) route_scatter_kernel(const T* __restrict_
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128) route_gather_kernel(const T* __restrict__ ys, const int* __restrict__ row_of_pair,
+__global__ void __launch_bounds__(256) route_gather_kernel(const T* __restrict__ ys, const int* __restrict__ row_of_pair,
                                                            T* __restrict__ out, int dim, int top, int n_pairs) {
   pdl_launch_dependents();
   pdl_wait();
+  extern __shared__ int rows_of_token[];
   const int t = blockIdx.x;
+  for (int k = threadIdx.x; k < top; k += blockDim.x) rows_of_token[k] = ld_fresh(row_of_pair + (size_t)t * top + k);
+  __syncthreads();
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     float a = 0.f;
     for (int k = 0; k < top; ++k) {
-      const int row = ld_fresh(row_of_pair + (size_t)t * top + k);
+      const int row = rows_of_token[k];
       if (FMS_IN(row, n_pairs)) a += to_f32(ys[(size_t)row * dim + d]);
     }
     out[(size_t)t * dim + d] = from_f32<T>(a);
@@ -398,7 +433,7 @@ FMS_API int fms_route(const void* x, int dtype, const void* router, int router_d
   if (smem > 200 * 1024) return fms_fail("route: rows of %d values and %d experts do not fit shared memory", dim, experts);
   FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(router_dtype, TW, {
     if (smem > 48 * 1024) cudaFuncSetAttribute(route_kernel<T, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    fms_launch(route_kernel<T, TW>, dim3(n_tokens), dim3(128), smem, stream, (const T*)x, (const TW*)router, expert, weight,
+    fms_launch(route_kernel<T, TW>, dim3(n_tokens), dim3(32 * ROUTE_WARPS), smem, stream, (const T*)x, (const TW*)router, expert, weight,
                dim, experts, top);
   }));
   if (fms_launch_status("route")) return 1;
@@ -416,6 +451,13 @@ FMS_API int fms_route(const void* x, int dtype, const void* router, int router_d
 FMS_API int fms_gated_clamped(const void* gu, void* out, int dtype, int n_rows, int hidden, float limit, float alpha,
                               cudaStream_t stream) {
   if (n_rows <= 0 || hidden <= 0) return 0;
+  if (dtype == FMS_BF16 && hidden % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const long total8 = (long)n_rows * (hidden / 8);
+    const int blocks8 = (int)((total8 + 255) / 256 < 148 * 32 ? (total8 + 255) / 256 : 148 * 32);
+    fms_launch(gated_clamped_vec_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+               hidden, limit, alpha, n_rows);
+    return fms_launch_status("gated_clamped");
+  }
   const size_t total = (size_t)n_rows * hidden;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   FMS_DISPATCH_DTYPE(dtype, T,
@@ -428,7 +470,7 @@ FMS_API int fms_route_gather(const void* ys, int dtype, const int* row_of_pair, 
                              cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   FMS_DISPATCH_DTYPE(dtype, T,
-                     fms_launch(route_gather_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, (const T*)ys, row_of_pair,
+                     fms_launch(route_gather_kernel<T>, dim3(n_tokens), dim3(256), sizeof(int) * top, stream, (const T*)ys, row_of_pair,
                                 (T*)out, dim, top, n_tokens * top));
   return fms_launch_status("route_gather");
 }

@@ -263,6 +263,8 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(LatentArgs a) {
 // row width; (B) eight threads a row take the running maximum, the probabilities (bfloat16, as in every
 // flash-attention kernel) and the sum; (C) warp w adds P . c for 16 rows and a quarter of the latent's columns
 // (rank / 4, its share of the accumulator in registers), c being read as it lies in the key tile.
+// With n_splits > 1 (a decode step: tq = 1, the block's rows are one token's heads) block z takes the keys of split z
+// (SPLIT keys) and leaves its unnormed sums, maximum and sum for latent_combine_kernel.
 constexpr int MR = 32, MK = 32;
 
 __device__ __forceinline__ void lat_mma(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
@@ -303,6 +305,7 @@ __global__ void __launch_bounds__(256) latent_prefill_mma_kernel(LatentArgs a, c
   pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int seq = tiles[2 * blockIdx.x], r0 = tiles[2 * blockIdx.x + 1], h0 = blockIdx.y * hb;
+  const int split = blockIdx.z;
   if (!FMS_IN(seq, a.n_seqs)) return;
   const int slot = a.slots[seq];
   if (!FMS_IN(slot, a.n_slots)) return;
@@ -310,6 +313,9 @@ __global__ void __launch_bounds__(256) latent_prefill_mma_kernel(LatentArgs a, c
   const int ntok = min(tq, first_row[seq + 1] - first);
   if (ntok <= 0) return;
   const int last_pos = ld_fresh(a.positions + first + ntok - 1);
+  const int kt_lo = a.n_splits > 1 ? split * (SPLIT / MK) : 0;
+  const int n_kt = a.n_splits > 1 ? min(last_pos / MK + 1, kt_lo + SPLIT / MK) : last_pos / MK + 1;
+  if (kt_lo >= n_kt) return;  // a split beyond the sequence: the merge does not look at it
   if (tid < MR) {
     const int tok = tid / hb, hh = tid - tok * hb;
     pos_s[tid] = (tok < ntok && h0 + hh < a.heads) ? ld_fresh(a.positions + first + tok) : -1;
@@ -337,13 +343,12 @@ __global__ void __launch_bounds__(256) latent_prefill_mma_kernel(LatentArgs a, c
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
-  load_keys(0);  // one group: the queries and the first keys
+  load_keys(kt_lo);  // one group: the queries and the first keys
   float acc[NT][4];
 #pragma unroll
   for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   const int rg = warp & 1, part = warp >> 1;
-  const int n_kt = last_pos / MK + 1;
-  for (int kt = 0; kt < n_kt; ++kt) {
+  for (int kt = kt_lo; kt < n_kt; ++kt) {
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();  // tile kt is in place for everyone, and everyone is done with the other stage
     if (kt + 1 < n_kt) load_keys(kt + 1);
@@ -422,6 +427,23 @@ __global__ void __launch_bounds__(256) latent_prefill_mma_kernel(LatentArgs a, c
       }
     }
   }
+  if (a.n_splits > 1) {  // unnormed sums, maximum and sum of this split, for the merge
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = rg * 16 + (lane >> 2) + 8 * half;
+      if (pos_s[r] < 0) continue;
+      const int tok = r / hb, h = h0 + r - tok * hb;
+      const size_t at = ((size_t)(first + tok) * a.heads + h) * a.n_splits + split;
+      if (part == 0 && (lane & 3) == 0) {
+        a.part_ml[2 * at] = m_s[r];
+        a.part_ml[2 * at + 1] = l_s[r];
+      }
+      float* o = a.part_o + at * a.rank + part * NT * 8 + 2 * (lane & 3);
+#pragma unroll
+      for (int i = 0; i < NT; ++i) *reinterpret_cast<float2*>(o + i * 8) = make_float2(acc[i][2 * half], acc[i][2 * half + 1]);
+    }
+    return;
+  }
   __syncthreads();
   if (tid < MR) {  // what each row's sums are multiplied by: the softmax's denominator with the sink, and the gate
     float f = 0.f;
@@ -469,7 +491,8 @@ int launch_attention(const LatentArgs& a, int n_tokens, cudaStream_t stream) {
   if (a.rank <= 128) FMS_LATENT_LAUNCH(4);
   else if (a.rank <= 256) FMS_LATENT_LAUNCH(8);
   else if (a.rank <= 512) FMS_LATENT_LAUNCH(16);
-  else return fms_fail("latent_attention: a latent of %d values is more than the kernel keeps (512)", a.rank);
+  else if (a.rank <= 1024) FMS_LATENT_LAUNCH(32);
+  else return fms_fail("latent_attention: a latent of %d values is more than the kernel keeps (1024)", a.rank);
 #undef FMS_LATENT_LAUNCH
   if (fms_launch_status("latent_attention")) return 1;
   if (a.n_splits > 1) {
@@ -526,19 +549,23 @@ FMS_API int fms_latent_attention_prefill_bf16(const void* q, void* out, const vo
                                               int block_tokens, const int* slots, const int* first_row,
                                               const int* positions, const int* tiles, int n_tiles, int tile_tokens,
                                               int heads_per_block, int heads, int rank, int rot, float scale, int n_seqs,
-                                              int n_slots, int n_blocks, cudaStream_t stream) {
+                                              int n_slots, int n_blocks, const int* token_seq, int n_splits, float* part_o,
+                                              float* part_ml, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (n_splits < 1 || (n_splits > 1 && (tile_tokens != 1 || part_o == nullptr || part_ml == nullptr || token_seq == nullptr)))
+    return fms_fail("latent_attention_prefill: %d splits need one token a tile and scratch", n_splits);
   const int width = rank + rot;
   if (rank % 64 || rank > 512 || width % 32 || tile_tokens * heads_per_block != MR)
     return fms_fail("latent_attention_prefill: rank %d, rot %d, %d tokens x %d heads a block", rank, rot, tile_tokens, heads_per_block);
   LatentArgs a;
   a.q = q; a.out = out; a.cache = cache; a.gate = gate; a.sink = sink; a.table = table; a.slots = slots;
-  a.token_seq = nullptr; a.positions = positions; a.part_o = nullptr; a.part_ml = nullptr; a.gate_stride = gate_stride;
+  a.token_seq = token_seq; a.positions = positions; a.part_o = part_o; a.part_ml = part_ml; a.gate_stride = gate_stride;
   a.table_stride = table_stride; a.block_tokens = block_tokens; a.heads = heads; a.rank = rank; a.rot = rot;
-  a.n_splits = 1; a.n_seqs = n_seqs; a.n_slots = n_slots; a.n_blocks = n_blocks; a.scale = scale;
+  a.n_splits = n_splits; a.n_seqs = n_seqs; a.n_slots = n_slots; a.n_blocks = n_blocks; a.scale = scale;
   const int rowb = width * 2 + 16;
   const size_t smem = (size_t)(MR + 2 * MK) * rowb + MR * (MK + 1) * 4 + MR * (MK * 2 + 16) + MR * 16;
-  dim3 grid(n_tiles, (heads + heads_per_block - 1) / heads_per_block);
+  dim3 grid(n_tiles, (heads + heads_per_block - 1) / heads_per_block, n_splits);
+  if (grid.z > 65535) return fms_fail("latent_attention_prefill: %d splits", n_splits);
 #define FMS_LATENT_MMA(NT)                                                                                              \
   case NT:                                                                                                              \
     if (sink && sink_dtype == FMS_F32) {                                                                                \
@@ -558,5 +585,13 @@ FMS_API int fms_latent_attention_prefill_bf16(const void* q, void* out, const vo
     default: return fms_fail("latent_attention_prefill: rank %d", rank);
   }
 #undef FMS_LATENT_MMA
-  return fms_launch_status("latent_attention_prefill");
+  if (fms_launch_status("latent_attention_prefill")) return 1;
+  if (n_splits > 1) {  // one token a tile: the rows of the merge are the step's rows, tile i being row i
+    if (sink && sink_dtype == FMS_F32)
+      fms_launch(latent_combine_kernel<__nv_bfloat16, float>, dim3(n_tiles, heads), dim3(128), 0, stream, a);
+    else
+      fms_launch(latent_combine_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(n_tiles, heads), dim3(128), 0, stream, a);
+    return fms_launch_status("latent_attention (combine)");
+  }
+  return 0;
 }

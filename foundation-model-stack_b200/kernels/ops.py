@@ -60,7 +60,7 @@ _SIGNATURES = {
     "fms_route_gather": [_P, _I, _P, _P, _I, _I, _I, _P],
     "fms_gated_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
     "fms_latent_attention_prefill_bf16": [_P, _P, _P, _P, _L, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
-                                          _F, _I, _I, _I, _P],
+                                          _F, _I, _I, _I, _P, _I, _P, _P, _P],
     "fms_latent_prepare": [_P, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
                            _I, _I, _P, _P],
     "fms_latent_attention": [_P, _P, _I, _P, _P, _L, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I,
@@ -684,15 +684,26 @@ def latent_attention(q_full: torch.Tensor, batch, view, gate: Optional[torch.Ten
     """Causal softmax attention of the step's rows over the cached latent rows [c | kr] (which already hold the step's
     own), with a per-head sink in the denominator and a per-head sigmoid gate on the result.  ``gate``: the matrix
     whose column ``gate_offset + h`` holds head h's gate logit of each row.  Returns [tokens, heads, rank]."""
-    global _latent_split
+    global _latent_split, launches
     n = q_full.shape[0]
     out = torch.empty((n, heads, rank), dtype=q_full.dtype, device=q_full.device)
-    if (USE_LATENT_MMA and not batch.decode and q_full.dtype == torch.bfloat16 and rank % 64 == 0 and rank <= 512
+    if _latent_split is None:
+        _latent_split = int(load_library("latent_attention").fms_latent_split_tokens())
+    if (USE_LATENT_MMA and q_full.dtype == torch.bfloat16 and rank % 64 == 0 and rank <= 512
             and (rank + rot) % 32 == 0 and (gate is None or gate.dtype == torch.bfloat16)):
-        # a prompt's rows: both products on the tensor cores, 32 rows (tokens x heads) a block
-        heads_per_block = 1
-        while heads_per_block < min(32, heads):
-            heads_per_block *= 2
+        # both products on the tensor cores, 32 rows a block: a prompt's rows as tokens x heads over all their keys; a
+        # decode step's as one token's heads over one split of the keys, merged afterwards
+        n_splits, part_o, part_ml = 1, None, None
+        if batch.decode:
+            heads_per_block = 32
+            n_splits = max(1, (batch.max_len_after + _latent_split - 1) // _latent_split)
+            if n_splits > 1:
+                part_o = torch.empty((n, heads, n_splits, rank), dtype=torch.float32, device=q_full.device)
+                part_ml = torch.empty((n, heads, n_splits, 2), dtype=torch.float32, device=q_full.device)
+        else:
+            heads_per_block = 1
+            while heads_per_block < min(32, heads):
+                heads_per_block *= 2
         tile_tokens = 32 // heads_per_block
         tiles = batch.query_tiles(tile_tokens)
         gate_ptr = None if gate is None else _ptr(gate) + gate_offset * gate.element_size()
@@ -700,12 +711,13 @@ def latent_attention(q_full: torch.Tensor, batch, view, gate: Optional[torch.Ten
               0 if gate is None else gate.shape[1], _ptr(sink), _code(sink.dtype) if sink is not None else F32,
               _ptr(view.table), view.table.shape[1], view.block_tokens, _ptr(batch.slots), _ptr(batch.first_row),
               _ptr(batch.positions), _ptr(tiles), tiles.shape[0], tile_tokens, heads_per_block, heads, rank, rot,
-              float(scale), batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())
+              float(scale), batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _ptr(batch.token_seq), n_splits,
+              _ptr(part_o), _ptr(part_ml), _stream())
+        if n_splits > 1:
+            launches += 1
         return out
     n_splits, part_o, part_ml = 1, None, None
     if batch.decode:
-        if _latent_split is None:
-            _latent_split = int(load_library("latent_attention").fms_latent_split_tokens())
         n_splits = max(1, (batch.max_len_after + _latent_split - 1) // _latent_split)
         if n_splits > 1:
             part_o = torch.empty((n, heads, n_splits, rank), dtype=torch.float32, device=q_full.device)
@@ -717,7 +729,6 @@ def latent_attention(q_full: torch.Tensor, batch, view, gate: Optional[torch.Ten
           _ptr(batch.positions), n, n_splits, _ptr(part_o), _ptr(part_ml), heads, rank, rot, float(scale),
           batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())
     if n_splits > 1:
-        global launches
         launches += 1
     return out
 
