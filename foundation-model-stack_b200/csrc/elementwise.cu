@@ -324,6 +324,51 @@ __global__ void normed_add_rmsnorm_kernel(float* residual, const T* delta, int h
   }
 }
 
+// The same with the row in registers: NPER values a thread (dim <= NPER * blockDim), every value read once.
+template <typename T, typename TG, int NPER>
+__global__ void normed_add_rmsnorm_regs_kernel(float* residual, const T* delta, int has_post, const TG* post_gain_vec,
+                                               float post_gain, float post_eps, const TG* gain_vec, float gain, float eps,
+                                               T* out, const int* rows, int dim, int residual_rows) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  if (!FMS_IN(src, residual_rows)) return;  // the whole block alike
+  float* res = residual + (size_t)src * dim;
+  const T* del = delta ? delta + (size_t)src * dim : nullptr;
+  float x[NPER], v[NPER];
+  float sd = 0.f;
+#pragma unroll
+  for (int j = 0; j < NPER; ++j) {
+    const int d = threadIdx.x + j * blockDim.x;
+    x[j] = d < dim ? res[d] : 0.f;
+    v[j] = (del && d < dim) ? to_f32(del[d]) : 0.f;
+    sd += v[j] * v[j];
+  }
+  float inv_d = 1.f;
+  if (del && has_post) inv_d = 1.f / sqrtf(block_sum(sd, scratch) / (float)dim + post_eps);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NPER; ++j) {
+    const int d = threadIdx.x + j * blockDim.x;
+    if (d < dim && del) {
+      float add = v[j];
+      if (has_post) add = add * inv_d * (post_gain_vec ? to_f32(post_gain_vec[d]) : post_gain);
+      x[j] += add;
+      if (rows == nullptr) res[d] = x[j];
+    }
+    ss += x[j] * x[j];
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+  T* o = out + (size_t)r * dim;
+#pragma unroll
+  for (int j = 0; j < NPER; ++j) {
+    const int d = threadIdx.x + j * blockDim.x;
+    if (d < dim) o[d] = from_f32<T>(x[j] * inv * (gain_vec ? to_f32(gain_vec[d]) : gain));
+  }
+}
+
 FMS_API int fms_normed_add_rmsnorm(float* residual, const void* delta, int has_post, const void* post_gain_vec,
                                    float post_gain, float post_eps, const void* gain_vec, float gain, float eps,
                                    int gain_dtype, void* out, int dtype, const int* rows, int n_rows, int dim,
@@ -331,6 +376,24 @@ FMS_API int fms_normed_add_rmsnorm(float* residual, const void* delta, int has_p
   if (n_rows <= 0) return 0;
   if (dim <= 0) return fms_fail("normed_add_rmsnorm: dim %d", dim);
   const int threads = dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128));
+  if (dim <= 8 * threads) {  // the row fits the block's registers
+    const int nper = (dim + threads - 1) / threads;
+    FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG, {
+      if (nper <= 2)
+        fms_launch(normed_add_rmsnorm_regs_kernel<T, TG, 2>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta,
+                   has_post, (const TG*)post_gain_vec, post_gain, post_eps, (const TG*)gain_vec, gain, eps, (T*)out, rows, dim,
+                   residual_rows);
+      else if (nper <= 4)
+        fms_launch(normed_add_rmsnorm_regs_kernel<T, TG, 4>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta,
+                   has_post, (const TG*)post_gain_vec, post_gain, post_eps, (const TG*)gain_vec, gain, eps, (T*)out, rows, dim,
+                   residual_rows);
+      else
+        fms_launch(normed_add_rmsnorm_regs_kernel<T, TG, 8>, dim3(n_rows), dim3(threads), 0, stream, residual, (const T*)delta,
+                   has_post, (const TG*)post_gain_vec, post_gain, post_eps, (const TG*)gain_vec, gain, eps, (T*)out, rows, dim,
+                   residual_rows);
+    }));
+    return fms_launch_status("normed_add_rmsnorm");
+  }
   FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG,
                      fms_launch(normed_add_rmsnorm_kernel<T, TG>, dim3(n_rows), dim3(threads), 0, stream, residual,
                                 (const T*)delta, has_post, (const TG*)post_gain_vec, post_gain, post_eps,

@@ -8,7 +8,7 @@
 // holds (zero for a new sequence) and is written back after the step's last token.
 //
 // Two ways through a step.  Few tokens a sequence (decode, short continuations): one thread per (sequence, channel)
-// walks the tokens in order.  Many tokens: the tokens are cut into chunks of CHUNK; S_t = a_t S_(t-1) + b_t is a
+// walks the tokens in order.  Many tokens: the tokens are cut into chunks of CHUNK (32); S_t = a_t S_(t-1) + b_t is a
 // composition of affine maps, so (1) every (chunk, channel) composes its own maps into one (A, B) from a zero
 // start, (2) one thread per (sequence, channel) walks the chunks in order and leaves every chunk's start state,
 // (3) every (chunk, channel) walks its tokens again from that start state and writes y.  The chunk boundaries
@@ -25,7 +25,7 @@ __device__ __forceinline__ int ld_fresh(const int* p) { return __ldcg(p); }
 __device__ __forceinline__ float ld_fresh(const float* p) { return __ldcg(p); }
 
 namespace {
-constexpr int CHUNK = 64;
+constexpr int CHUNK = 32;
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 __device__ __forceinline__ float mingru_candidate(float u) { return u >= 0.f ? u + 0.5f : sigmoid_f(u); }
