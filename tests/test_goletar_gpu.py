@@ -354,7 +354,7 @@ def test_unequal_batches_freed_slots_and_poisoned_blocks(folders, oracles, which
     cfg = gm.CONFIGS[which]
     engine = model_of(folders, which, dtype).new_engine(max_tokens=64 * 12, max_slots=5, sampling=False)
     for round_ in range(2):
-        lengths, extra = ((1, 70, 5, 131, 64), (3, 9, 0, 12, 12)) if round_ == 0 else ((128, 2, 33), (5, 5, 1))
+        lengths, extra = ((1, 70, 5, 131, 64), (3, 9, 0, 12, 12)) if round_ == 0 else ((210, 2, 33), (5, 5, 1))
         full = [gm.prompt(cfg, n + e, 50 + 10 * round_ + i) for i, (n, e) in enumerate(zip(lengths, extra))]
         slots = engine.begin(len(lengths))
         got = [[] for _ in lengths]
