@@ -161,7 +161,8 @@ class StateGroup:
 class Cache:
     """Slots, lengths and the storage groups of one model.
 
-    ``layer_requests[i]`` is what layer i's mixer asks for (None: nothing).  ``max_tokens`` is the most
+    ``layer_requests[i]`` is what layer i's mixer asks for (None: nothing; a tuple: several things, and the layer's
+    view is then the tuple of their views).  ``max_tokens`` is the most
     tokens that live sequences hold at any time, each sequence's count rounded up to a multiple of 64.
     ``named_requests``: what parts outside the layers ask for (the embedding's state of a sequence), by a name under
     which ``layer_view(name)`` finds it.
@@ -189,8 +190,17 @@ class Cache:
         self.groups: List[Union[KVGroup, StateGroup]] = []
         self._group_of_layer: Dict[Union[int, str], Union[KVGroup, StateGroup]] = {}
         by_request: Dict[object, List[int]] = {}
+        self._parts_of_layer: Dict[Union[int, str], int] = {}  # layers whose mixer asked for several things at once
         for layer, req in list(enumerate(layer_requests)) + list((named_requests or {}).items()):
-            if req is not None:
+            if isinstance(req, (tuple, list)):
+                # a mixer made of several (attention beside a recurrence, a state matrix beside a convolution's
+                # tail): every request gets storage of its own kind under the key (layer, index), and the layer's
+                # view is the tuple of their views, in the order of the requests
+                self._parts_of_layer[layer] = len(req)
+                for j, r in enumerate(req):
+                    if r is not None:
+                        by_request.setdefault(r, []).append((layer, j))
+            elif req is not None:
                 by_request.setdefault(req, []).append(layer)
         for req, layers in by_request.items():
             if isinstance(req, KVRequest):
@@ -293,6 +303,8 @@ class Cache:
         return self.position[slot] - self.length[slot]
 
     def layer_view(self, layer: Union[int, str]):
+        if layer in self._parts_of_layer:
+            return tuple(self.layer_view((layer, j)) for j in range(self._parts_of_layer[layer]))
         g = self._group_of_layer.get(layer)
         return None if g is None else g.view(layer)
 

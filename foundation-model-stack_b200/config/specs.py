@@ -70,7 +70,9 @@ class FeedForwardSpec:
 class BlockSpec:
     """One layer: its norms, mixer and feed-forward and their arrangement, which names the block class in the
     registry (``fms_b200.parts.register_block``).  ``arrangement == "pre_norm"``:
-    x += mixer(norm1(x)); x += feed_forward(norm2(x)).  ``arrangement == "sandwich"``: every sublayer's output is
+    x += mixer(norm1(x)); x += feed_forward(norm2(x)).  ``arrangement == "post_norm"``: the norm follows the sum and
+    the sublayers read the stream itself, x = norm1(alpha x + mixer(x)); x = norm2(alpha x + feed_forward(x)), with
+    ``alpha`` in ``options``.  ``arrangement == "sandwich"``: every sublayer's output is
     normed once more before it is added, x += norm1b(mixer(norm1(x))); x += norm2b(feed_forward(norm2(x))); the two
     further norms are ``mixer_post_norm`` and ``feed_forward_post_norm``, and a layer without a feed-forward
     (``feed_forward is None``) ends after its mixer.  The names are those under which the layer's
@@ -87,6 +89,9 @@ class BlockSpec:
     mixer_post_norm: Optional[NormSpec] = None
     feed_forward_post_norm: Optional[NormSpec] = None
     post_names: Tuple[str, str] = ("post_ln", "ff_post_ln")
+    # the layer has no tensors of its own: it runs with the parts (mixer, feed-forward, norms) of that earlier layer,
+    # whose spec its own equals, and with a cache entry or state of its own
+    weights_of: Optional[int] = None
 
 
 @dataclasses.dataclass(frozen=True)
@@ -131,6 +136,10 @@ class DecoderSpec:
 
     def __post_init__(self):
         n = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            j = layer.weights_of
+            if j is not None and not (0 <= j < i and self.layers[j].weights_of is None):
+                raise ValueError(f"layer {i} takes the weights of layer {j}, which is no earlier layer with weights of its own")
         for call in self.schedule:
             if not (0 <= call.layer < n and 0 <= call.cache_layer < n):
                 raise ValueError(f"schedule entry {call} names a layer outside 0..{n - 1}")

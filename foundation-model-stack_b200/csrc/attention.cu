@@ -57,6 +57,9 @@ struct AttnArgs {
   int window;
   int table_rows;   // slots the table has rows for, and blocks in the cache: extents that only the bounds-checked
   int pool_blocks;  // build looks at (0: not known)
+  // [nheads] float32 or null.  A sink is a term exp(sink[head]) in the softmax's denominator that belongs to no key:
+  // it has no value, is not multiplied by the scale, and counts once however the keys are cut into tiles or splits.
+  const float* sink;
 };
 
 // The cache block that holds key block kb of the sequence in `slot`; negative: none (a block given back behind a
@@ -179,6 +182,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a, const int
   }
   if (row_ok) {
     T* o = (T*)a.out + (size_t)(row_begin + r0 + r) * a.nheads * HD + (size_t)head * HD;
+    if (a.sink != nullptr) l += expf(a.sink[head] - (m == -INFINITY ? 0.f : m));
     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) o[c + 8 * j] = from_f32<T>(acc[j] * inv);
@@ -383,6 +387,7 @@ __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o
   for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, pair_of(s).x);
   float total = 0.f;
   for (int s = s_lo; s <= s_hi; ++s) total += pair_of(s).y * expf(pair_of(s).x - m);
+  if (a.sink != nullptr) total += expf(a.sink[head] - (m == -INFINITY ? 0.f : m));
   const float inv = total > 0.f ? 1.f / total : 0.f;
   float sum = 0.f;
 #pragma unroll
@@ -546,15 +551,15 @@ FMS_API int fms_attn_prefill_tile_positions(int dtype, int nheads, int kvheads) 
   return TQ;
 }
 
-FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const void* keys, const void* values,
-                                  const int* table, int table_stride, int block_tokens, const int* slots,
-                                  const int* first_row, const int* len_after, const int* tiles, int n_tiles,
-                                  int nheads, int kvheads, int head_dim, float scale, int window, int pool_blocks,
-                                  int table_rows, int* error_flag, cudaStream_t stream) {
+static int attention_prefill(const void* q, void* out, int dtype, const void* keys, const void* values,
+                             const int* table, int table_stride, int block_tokens, const int* slots,
+                             const int* first_row, const int* len_after, const int* tiles, int n_tiles,
+                             int nheads, int kvheads, int head_dim, float scale, int window, int pool_blocks,
+                             int table_rows, int* error_flag, const float* sink, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (check_args("attention_prefill", nheads, kvheads, head_dim, block_tokens)) return 1;
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window,
-             table_rows, pool_blocks};
+             table_rows, pool_blocks, sink};
   if (nheads > 65535) return fms_fail("attention_prefill: %d heads", nheads);
   if (!(scale > 0.f)) return fms_fail("attention_prefill: the scale of the scores is %g; it must be positive", (double)scale);
 #if FMS_ATTENTION_TC
@@ -604,6 +609,27 @@ FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const voi
   return fms_launch_status("attention_prefill");
 }
 
+FMS_API int fms_attention_prefill(const void* q, void* out, int dtype, const void* keys, const void* values,
+                                  const int* table, int table_stride, int block_tokens, const int* slots,
+                                  const int* first_row, const int* len_after, const int* tiles, int n_tiles,
+                                  int nheads, int kvheads, int head_dim, float scale, int window, int pool_blocks,
+                                  int table_rows, int* error_flag, cudaStream_t stream) {
+  return attention_prefill(q, out, dtype, keys, values, table, table_stride, block_tokens, slots, first_row, len_after,
+                           tiles, n_tiles, nheads, kvheads, head_dim, scale, window, pool_blocks, table_rows, error_flag,
+                           nullptr, stream);
+}
+
+// The same with a sink per head in the softmax's denominator (sink: [nheads] float32 on the device).
+FMS_API int fms_attention_prefill_sink(const void* q, void* out, int dtype, const void* keys, const void* values,
+                                       const int* table, int table_stride, int block_tokens, const int* slots,
+                                       const int* first_row, const int* len_after, const int* tiles, int n_tiles,
+                                       int nheads, int kvheads, int head_dim, float scale, int window, int pool_blocks,
+                                       int table_rows, int* error_flag, const float* sink, cudaStream_t stream) {
+  return attention_prefill(q, out, dtype, keys, values, table, table_stride, block_tokens, slots, first_row, len_after,
+                           tiles, n_tiles, nheads, kvheads, head_dim, scale, window, pool_blocks, table_rows, error_flag,
+                           sink, stream);
+}
+
 // part_o: float [seqs, nheads, n_splits, HD]; part_ml: float [seqs, nheads, n_splits, 2]; both scratch.
 // pool_blocks: blocks in the cache (bounds the early L2 hints and the streaming kernel's tensor maps; 0 turns both
 // off).  table_rows: slots the table has rows for (looked at by the bounds-checked build only; 0: not known).  total_len: cached tokens of all sequences together as far as the host knows (0: unknown), by which the
@@ -621,7 +647,22 @@ FMS_API int fms_attention_decode(const void* q, void* out, int dtype, const void
   if (check_args("attention_decode", nheads, kvheads, head_dim, block_tokens)) return 1;
   if (!(scale > 0.f)) return fms_fail("attention_decode: the scale of the scores is %g; it must be positive", (double)scale);
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window,
-             table_rows, pool_blocks};
+             table_rows, pool_blocks, nullptr};
+  return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, pool_blocks, total_len, work_counter, error_flag, stream);
+}
+
+// The same with a sink per head in the softmax's denominator (sink: [nheads] float32 on the device).
+FMS_API int fms_attention_decode_sink(const void* q, void* out, int dtype, const void* keys, const void* values,
+                                      const int* table, int table_stride, int block_tokens, const int* slots,
+                                      const int* first_row, const int* len_after, int n_seqs, int n_splits, float* part_o,
+                                      float* part_ml, int nheads, int kvheads, int head_dim, float scale, int window,
+                                      int pool_blocks, int table_rows, long total_len, int* work_counter, int* error_flag,
+                                      const float* sink, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (check_args("attention_decode", nheads, kvheads, head_dim, block_tokens)) return 1;
+  if (!(scale > 0.f)) return fms_fail("attention_decode: the scale of the scores is %g; it must be positive", (double)scale);
+  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window,
+             table_rows, pool_blocks, sink};
   return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, pool_blocks, total_len, work_counter, error_flag, stream);
 }
 
@@ -680,6 +721,6 @@ FMS_API int fms_attention_decode_no_alloc(const void* q, void* out, int dtype, c
   if (scratch == nullptr) return 1;
   float* part_o = scratch;                  // [seqs, nheads, n_splits, HD]
   float* part_ml = scratch + entries * HD;  // [seqs, nheads, n_splits, 2]
-  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window, 0, 0};
+  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window, 0, 0, nullptr};
   return launch_decode("attention_decode_no_alloc", a, dtype, n_seqs, n_splits, part_o, part_ml, 0, 0, nullptr, nullptr, stream);
 }

@@ -349,6 +349,7 @@ __global__ void __launch_bounds__(NW * 32, WK == 32 ? 16 / NW : 12 / NW)
     const size_t at = ((size_t)seq * a.nheads + head) * n_splits + split;
     if (n_splits == 1) {  // nothing to merge with: this is the result (no second kernel is launched)
       __nv_bfloat16* out = (__nv_bfloat16*)a.out + (size_t)a.first_row[seq] * a.nheads * HD + (size_t)head * HD;
+      if (a.sink != nullptr) lsum += exp2f(a.sink[head] * LOG2E - (mm == -INFINITY ? 0.f : mm));  // mm is in base 2
       const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
       for (int d = tid % TPH; d < HD; d += TPH) {
         float sum = 0.f;
@@ -532,6 +533,10 @@ __global__ void __launch_bounds__(PF_WARPS * 32, HD <= 128 ? 3 : 1) attn_prefill
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (!row_ok[h]) continue;
+    if (a.sink != nullptr) {  // m is in base 2
+      const int r = warp * 16 + g + 8 * h;
+      l[h] += exp2f(a.sink[kvh * group + g0 + (r - (r / gh) * gh)] * LOG2E - (m[h] == -INFINITY ? 0.f : m[h]));
+    }
     const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j)

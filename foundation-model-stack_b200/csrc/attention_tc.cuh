@@ -266,6 +266,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     }
     if (ok && __all_sync(0xffffffffu, wait_or_abort(&o_done[(nblocks - 1) & 1], ((nblocks - 1) >> 1) & 1, failed))) {
       tc_fence_after();
+      if (a.sink != nullptr && row_ok) l += exp2f(a.sink[kvh * group + g0 + gi] * LOG2E - (m_ref == -INFINITY ? 0.f : m_ref));
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* o_row = (__nv_bfloat16*)a.out +
                              ((size_t)(row_begin + r0 + (row_ok ? pi : 0)) * a.nheads + kvh * group + g0 + (row_ok ? gi : 0)) * HD;

@@ -684,3 +684,194 @@ FMS_API int fms_decode_advance(int* positions, int* lengths, const int* offsets,
              slots, spare_slot, n);
   return fms_launch_status("decode_advance");
 }
+
+// ---------------------------------------------------------------------------------------------------
+// norm after the sum (a layer whose norm follows the residual sum instead of preceding the sublayer):
+//   x = alpha * residual[r] + sa * da[r] (+ sb * db[r]);  y = x / sqrt(mean(x^2) + eps) * gain
+//   residual[r] = y (float32, in place);  copy[r] = y in the compute dtype, where a copy is asked for
+// The sublayer's output may come as two parts with a factor each (two mixers side by side).  One block per row.
+// No pointer is declared __restrict__ and nothing is read ahead of griddepcontrol.wait.
+// ---------------------------------------------------------------------------------------------------
+template <typename T, typename TG>
+__global__ void scaled_add_rmsnorm_kernel(float* residual, float alpha, const T* da, float sa, const T* db, float sb,
+                                          const TG* gain, float eps, T* copy, int dim) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * dim;
+  float* res = residual + base;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    float x = alpha * res[d];
+    if (da) x = fmaf(sa, to_f32(da[base + d]), x);
+    if (db) x = fmaf(sb, to_f32(db[base + d]), x);
+    res[d] = x;
+    ss += x * x;
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    const float y = res[d] * inv * to_f32(gain[d]);  // this thread's own earlier store
+    res[d] = y;
+    if (copy) copy[base + d] = from_f32<T>(y);
+  }
+}
+
+FMS_API int fms_scaled_add_rmsnorm(float* residual, float alpha, const void* da, float sa, const void* db, float sb,
+                                   const void* gain, int gain_dtype, float eps, void* copy, int dtype, int n_rows, int dim,
+                                   cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dim <= 0) return fms_fail("scaled_add_rmsnorm: dim %d", dim);
+  const int threads = dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128));
+  FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG,
+                     fms_launch(scaled_add_rmsnorm_kernel<T, TG>, dim3(n_rows), dim3(threads), 0, stream, residual, alpha,
+                                (const T*)da, sa, (const T*)db, sb, (const TG*)gain, eps, (T*)copy, dim)));
+  return fms_launch_status("scaled_add_rmsnorm");
+}
+
+// float32 rows in the compute dtype (the stream as a sublayer's input where nothing else has made that copy)
+template <typename T>
+__global__ void cast_rows_kernel(const float* x, T* out, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = from_f32<T>(x[i]);
+}
+
+FMS_API int fms_cast_rows(const float* x, void* out, int dtype, long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(cast_rows_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x,
+                                          (T*)out, (size_t)n));
+  return fms_launch_status("cast_rows");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// queries, keys and values of a step on their way into attention, for heads whose first `rot` values are rotated,
+// whose queries and keys may be divided by their root mean square afterwards, and whose value size may differ from
+// the key size:
+//   proj[t] = [q: nheads x dim | k: kvheads x dim | v: kvheads x vdim | ...]   (row stride `stride`)
+//   q, k: pairs (2i, 2i+1), i < rot / 2, rotated by position * inv_freq[i]; the other values pass
+//   q, k: x / sqrt(mean(x^2) + eps) over the head's dim values, where qk_norm is set (no gain)
+//   q -> q_out[t, head, 0..pad) ; k, v -> the cache row of the token's slot and place, each `pad` wide:
+//   values beyond dim (vdim) are zeros, so that kernels built for one head size `pad` serve both
+// One block per token, a warp per head; float32 arithmetic.
+// ---------------------------------------------------------------------------------------------------
+constexpr int PREP_MAX_PAIRS = 256;
+
+template <typename T>
+__global__ void qk_prepare_store_kernel(const T* proj, int stride, T* q_out, const float* inv_freq, int rot,
+                                        int qk_norm, float eps, const int* positions, const int* position_ids,
+                                        const int* token_seq, const int* slots, T* k_cache, T* v_cache, const int* table,
+                                        int table_stride, int block_tokens, int nheads, int kvheads, int dim, int vdim,
+                                        int pad, int write_cache, int* error_flag, int n_seqs, int table_rows,
+                                        int pool_blocks) {
+  __shared__ float2 sc[PREP_MAX_PAIRS];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = __ldcg(positions + t);
+  const int pid = position_ids ? __ldcg(position_ids + t) : pos;
+  for (int i = threadIdx.x; i < rot / 2; i += blockDim.x) {
+    float s, c;
+    sincosf((float)pid * inv_freq[i], &s, &c);
+    sc[i] = make_float2(s, c);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const T* row = proj + (size_t)t * stride;
+  T* krow = nullptr;
+  T* vrow = nullptr;
+  if (write_cache) {
+    const int seq = token_seq[t];
+    if (FMS_IN(seq, n_seqs)) {
+      const int slot = __ldcg(slots + seq);
+      if (FMS_IN(slot, table_rows) && FMS_IN(pos / block_tokens, table_stride)) {
+        const int blk = table[(size_t)slot * table_stride + pos / block_tokens];
+        if (blk < 0) {
+          if (threadIdx.x == 0 && error_flag) atomicExch(error_flag, 2);
+        } else if (FMS_IN(blk, pool_blocks)) {
+          const size_t at = ((size_t)blk * kvheads * block_tokens + (pos % block_tokens)) * pad;
+          krow = k_cache + at;  // head h of this token: + h * block_tokens * pad
+          vrow = v_cache + at;
+        }
+      }
+    }
+  }
+  for (int item = warp; item < nheads + 2 * kvheads; item += nwarps) {
+    if (item >= nheads + kvheads) {  // a value head: copied and padded
+      const int h = item - nheads - kvheads;
+      if (vrow == nullptr) continue;
+      const T* src = row + (size_t)(nheads + kvheads) * dim + (size_t)h * vdim;
+      T* dst = vrow + (size_t)h * block_tokens * pad;
+      for (int e = lane; e < pad; e += 32) dst[e] = e < vdim ? src[e] : from_f32<T>(0.f);
+      continue;
+    }
+    const bool is_q = item < nheads;
+    const T* src = row + (size_t)item * dim;  // q heads, then k heads, all `dim` wide
+    T* dst = is_q ? q_out + ((size_t)t * nheads + item) * pad
+                  : (krow ? krow + (size_t)(item - nheads) * block_tokens * pad : nullptr);
+    if (dst == nullptr) continue;
+    float ss = 0.f;
+    for (int i = lane; i < rot / 2; i += 32) {
+      const float x0 = to_f32(src[2 * i]), x1 = to_f32(src[2 * i + 1]);
+      const float r0 = sc[i].y * x0 - sc[i].x * x1, r1 = sc[i].y * x1 + sc[i].x * x0;
+      ss += r0 * r0 + r1 * r1;
+    }
+    for (int e = rot + lane; e < dim; e += 32) {
+      const float x = to_f32(src[e]);
+      ss += x * x;
+    }
+    const float inv = qk_norm ? 1.f / sqrtf(warp_sum(ss) / (float)dim + eps) : 1.f;
+    for (int i = lane; i < rot / 2; i += 32) {
+      const float x0 = to_f32(src[2 * i]), x1 = to_f32(src[2 * i + 1]);
+      dst[2 * i] = from_f32<T>((sc[i].y * x0 - sc[i].x * x1) * inv);
+      dst[2 * i + 1] = from_f32<T>((sc[i].y * x1 + sc[i].x * x0) * inv);
+    }
+    for (int e = rot + lane; e < pad; e += 32) dst[e] = from_f32<T>(e < dim ? to_f32(src[e]) * inv : 0.f);
+  }
+}
+
+FMS_API int fms_qk_prepare_store(const void* proj, int dtype, int stride, void* q_out, const float* inv_freq, int rot,
+                                 int qk_norm, float eps, const int* positions, const int* position_ids,
+                                 const int* token_seq, const int* slots, void* k_cache, void* v_cache, const int* table,
+                                 int table_stride, int block_tokens, int n_tokens, int nheads, int kvheads, int dim,
+                                 int vdim, int pad, int write_cache, int* error_flag, int n_seqs, int table_rows,
+                                 int pool_blocks, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (rot < 0 || rot % 2 || rot > dim || rot / 2 > PREP_MAX_PAIRS || (rot > 0 && inv_freq == nullptr))
+    return fms_fail("qk_prepare_store: %d rotated values of %d", rot, dim);
+  if (dim <= 0 || vdim <= 0 || pad < dim || pad < vdim) return fms_fail("qk_prepare_store: dim %d, vdim %d, pad %d", dim, vdim, pad);
+  FMS_DISPATCH_DTYPE(dtype, T,
+                     fms_launch(qk_prepare_store_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, (const T*)proj, stride,
+                                (T*)q_out, inv_freq, rot, qk_norm, eps, positions, position_ids, token_seq, slots,
+                                (T*)k_cache, (T*)v_cache, table, table_stride, block_tokens, nheads, kvheads, dim, vdim, pad,
+                                write_cache, error_flag, n_seqs, table_rows, pool_blocks));
+  return fms_launch_status("qk_prepare_store");
+}
+
+// ---------------------------------------------------------------------------------------------------
+// gate on the heads' results: out[t, h * vdim + e] = factor * o[t, h * pad + e] * sigmoid(gate[t, h * vdim + e]),
+// e < vdim; o has rows of nheads * pad, gate is a run of columns of a wider matrix (row stride gate_stride)
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void sigmoid_gate_kernel(const T* o, const T* gate, int gate_stride, T* out, int nheads, int vdim, int pad,
+                                    float factor, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int width = nheads * vdim;
+  const size_t t = i / width;
+  const int c = (int)(i - t * width), h = c / vdim, e = c - h * vdim;
+  float v = to_f32(o[(t * nheads + h) * pad + e]) * factor;
+  if (gate) v *= 1.f / (1.f + expf(-to_f32(gate[t * gate_stride + c])));
+  out[i] = from_f32<T>(v);
+}
+
+FMS_API int fms_sigmoid_gate(const void* o, const void* gate, int gate_stride, void* out, int dtype, int n_tokens,
+                             int nheads, int vdim, int pad, float factor, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  const size_t total = (size_t)n_tokens * nheads * vdim;
+  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(sigmoid_gate_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                                          (const T*)o, (const T*)gate, gate_stride, (T*)out, nheads, vdim, pad, factor, total));
+  return fms_launch_status("sigmoid_gate");
+}

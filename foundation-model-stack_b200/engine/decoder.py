@@ -34,7 +34,12 @@ class Decoder(Part):
         emb_name, layers_name, norm_name, head_name = spec.names
         self.embedding = _add_path(self, emb_name, build_embedding(spec.embedding, spec.vocab_size, spec.dim))
         layer_list = _add_path(self, layers_name, Part())
-        self.blocks = [layer_list.add(str(i), build_block(b)) for i, b in enumerate(spec.layers)]
+        # a layer that takes another's weights is that layer's block once more (no child, so no tensors, of its own);
+        # the cache still gives every layer an entry of its own
+        self.blocks = []
+        for i, b in enumerate(spec.layers):
+            self.blocks.append(self.blocks[b.weights_of] if b.weights_of is not None
+                               else layer_list.add(str(i), build_block(b)))
         self.final_norm = _add_path(self, norm_name, build_norm(spec.final_norm))
         self.head = _add_path(self, head_name, Part())
         if not spec.tie_head:

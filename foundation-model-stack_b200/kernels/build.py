@@ -40,6 +40,7 @@ PLAIN_LIBRARIES = {
     "gemm_bf16_tc": ("gemm_bf16_tc.cu", []),
     "sampling": ("sampling.cu", []),
     "recurrent": ("recurrent.cu", []),
+    "state_scan": ("state_scan.cu", []),
     "grouped": ("grouped.cu", []),
     "latent_attention": ("latent_attention.cu", []),
 }

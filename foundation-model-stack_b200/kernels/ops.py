@@ -65,6 +65,19 @@ _SIGNATURES = {
                            _I, _I, _P, _P],
     "fms_latent_attention": [_P, _P, _I, _P, _P, _L, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I,
                              _I, _I, _P],
+    "fms_scaled_add_rmsnorm": [_P, _F, _P, _F, _P, _F, _P, _I, _F, _P, _I, _I, _I, _P],
+    "fms_cast_rows": [_P, _P, _I, _L, _P],
+    "fms_qk_prepare_store": [_P, _I, _I, _P, _P, _I, _I, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
+                             _P, _I, _I, _I, _P],
+    "fms_sigmoid_gate": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _P],
+    "fms_attention_prefill_sink": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P,
+                                   _P],
+    "fms_attention_decode_sink": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _I, _I, _L,
+                                  _P, _P, _P, _P],
+    "fms_causal_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "fms_selective_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "fms_delta_rule_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "fms_gated_group_rmsnorm": [_P, _P, _I, _I, _I, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
     "fms_attention_prefill": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P],
@@ -244,6 +257,32 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: tor
     out = torch.empty((n, dim), dtype=out_dtype, device=residual.device)
     _call("elementwise", "fms_add_rmsnorm", _ptr(residual), _ptr(delta), _ptr(gain), _code(gain.dtype), float(eps),
           _ptr(out), _code(out_dtype), _ptr(rows), n, dim, residual.shape[0], _stream())
+    return out
+
+
+def scaled_add_rmsnorm(residual: torch.Tensor, alpha: float, parts, gain: torch.Tensor, eps: float,
+                       out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    """The norm that follows the residual sum: residual (float32, in place) = gain * rmsnorm(alpha * residual +
+    sum of factor * delta over ``parts``, a list of one or two (delta, factor)).  Returns the new rows in ``out_dtype``
+    too, or None where that is float32 (the stream itself then serves)."""
+    n, dim = residual.shape
+    if residual.dtype != torch.float32:
+        raise KernelError("the residual stream is float32")
+    if not 1 <= len(parts) <= 2 or any(d.dtype != out_dtype or tuple(d.shape) != (n, dim) for d, _ in parts):
+        raise KernelError("scaled_add_rmsnorm: one or two sublayer outputs of the stream's shape, in the compute dtype")
+    (da, sa), (db, sb) = parts[0], (parts[1] if len(parts) > 1 else (None, 0.0))
+    copy = None if out_dtype == torch.float32 else torch.empty((n, dim), dtype=out_dtype, device=residual.device)
+    _call("elementwise", "fms_scaled_add_rmsnorm", _ptr(residual), float(alpha), _ptr(da), float(sa), _ptr(db), float(sb),
+          _ptr(gain), _code(gain.dtype), float(eps), _ptr(copy), _code(out_dtype), n, dim, _stream())
+    return copy
+
+
+def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Float32 rows in ``dtype`` (the same tensor where that is float32)."""
+    if dtype == torch.float32:
+        return x
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _call("elementwise", "fms_cast_rows", _ptr(x), _ptr(out), _code(dtype), x.numel(), _stream())
     return out
 
 
@@ -489,10 +528,46 @@ def attention_constants(head_dim: int, dtype: torch.dtype, nheads: int, kvheads:
     return _attn_constants[key]
 
 
+def qk_prepare_store(proj: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, qk_norm: bool, eps: float, batch,
+                     view, nheads: int, kvheads: int, dim: int, vdim: int, pad: int,
+                     writes_cache: bool = True) -> torch.Tensor:
+    """From rows [q: nheads x dim | k: kvheads x dim | v: kvheads x vdim | ...] of ``proj``: rotates the first ``rot``
+    values of every q and k head by the row's position (adjacent pairs), divides q and k by their root mean square
+    over ``dim`` where ``qk_norm``, writes k and v into the cache (heads of ``pad`` values there, zeros beyond dim and
+    vdim) and returns q [tokens, nheads * pad], padded alike."""
+    n = proj.shape[0]
+    if view.keys.dtype != proj.dtype or view.keys.shape[-1] != pad:
+        raise KernelError(f"cache is {view.keys.dtype} with heads of {view.keys.shape[-1]}, activations are {proj.dtype}, "
+                          f"heads of {pad}")
+    q = torch.empty((n, nheads * pad), dtype=proj.dtype, device=proj.device)
+    _call("elementwise", "fms_qk_prepare_store", _ptr(proj), _code(proj.dtype), proj.shape[1], _ptr(q), _ptr(inv_freq),
+          int(rot), 1 if qk_norm else 0, float(eps), _ptr(batch.positions), _ptr(getattr(batch, "position_ids", None)),
+          _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys), _ptr(view.values), _ptr(view.table),
+          view.table.shape[1], view.block_tokens, n, nheads, kvheads, dim, vdim, pad, 1 if writes_cache else 0,
+          _ptr(error_flag(proj.device)), batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())
+    return q
+
+
+def sigmoid_gate(o: torch.Tensor, gate: Optional[torch.Tensor], gate_offset: int, nheads: int, vdim: int, pad: int,
+                 factor: float = 1.0) -> torch.Tensor:
+    """out[t, h, :vdim] = factor * o[t, h, :vdim] * sigmoid(gate[t, gate_offset + h * vdim + :vdim]) for o with heads
+    of ``pad`` values; ``gate`` is a matrix whose columns from ``gate_offset`` on hold the gates' logits (None: no
+    gate, only the padding is dropped)."""
+    n = o.shape[0]
+    out = torch.empty((n, nheads * vdim), dtype=o.dtype, device=o.device)
+    gate_ptr = None if gate is None else _ptr(gate) + gate_offset * gate.element_size()
+    _call("elementwise", "fms_sigmoid_gate", _ptr(o), gate_ptr, 0 if gate is None else gate.shape[1], _ptr(out),
+          _code(o.dtype), n, nheads, vdim, pad, float(factor), _stream())
+    return out
+
+
 def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim: int, scale: float,
-              window: int) -> torch.Tensor:
+              window: int, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal softmax attention of the step's queries over the cache (which already holds the step's own
-    keys and values).  One query per sequence takes the split-key decode kernels, else the prefill kernel."""
+    keys and values).  One query per sequence takes the split-key decode kernels, else the prefill kernel.
+    ``sink`` [nheads] float32: a term exp(sink[h]) in every row's denominator that belongs to no key."""
+    if sink is not None and (sink.dtype != torch.float32 or sink.shape[0] != nheads):
+        raise KernelError("attention: the sinks are float32, one per head")
     out = torch.empty_like(q)
     lib = _attention_library(head_dim)
     split, tile_rows = attention_constants(head_dim, q.dtype, nheads, kvheads)
@@ -503,17 +578,21 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
         part_o = torch.empty((batch.n_seqs, nheads, n_splits, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((batch.n_seqs, nheads, n_splits, 2), dtype=torch.float32, device=q.device)
         # total_len (what the host knows of the sequences' lengths) chooses between the two bfloat16 decode kernels
-        _call(lib, "fms_attention_decode", *common, batch.n_seqs, n_splits, _ptr(part_o), _ptr(part_ml), nheads,
+        tail = () if sink is None else (_ptr(sink),)
+        _call(lib, "fms_attention_decode" if sink is None else "fms_attention_decode_sink", *common, batch.n_seqs,
+              n_splits, _ptr(part_o), _ptr(part_ml), nheads,
               kvheads, head_dim, float(scale), int(window), view.keys.shape[0], view.table.shape[0],
               int(getattr(batch, "total_len", 0)),
-              _ptr(_work_counter(q.device)), _ptr(error_flag(q.device)), _stream())
+              _ptr(_work_counter(q.device)), _ptr(error_flag(q.device)), *tail, _stream())
         if n_splits > 1 or q.dtype == torch.float32:
             global launches
             launches += 1  # the kernel that merges the splits
     else:
         tiles = batch.query_tiles(tile_rows)
-        _call(lib, "fms_attention_prefill", *common, _ptr(tiles), tiles.shape[0], nheads, kvheads, head_dim,
-              float(scale), int(window), view.keys.shape[0], view.table.shape[0], _ptr(error_flag(q.device)), _stream())
+        tail = () if sink is None else (_ptr(sink),)
+        _call(lib, "fms_attention_prefill" if sink is None else "fms_attention_prefill_sink", *common, _ptr(tiles),
+              tiles.shape[0], nheads, kvheads, head_dim, float(scale), int(window), view.keys.shape[0],
+              view.table.shape[0], _ptr(error_flag(q.device)), *tail, _stream())
     return out
 
 
@@ -563,6 +642,88 @@ def mingru_scan(proj: torch.Tensor, state: torch.Tensor, batch, width: int, writ
     global launches
     launches += 2 if n_chunks else 0
     return y
+
+
+# ---- state matrices carried from token to token -----------------------------------------------------
+def causal_conv(x: torch.Tensor, offset: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                tail: torch.Tensor, batch, activation: bool = True, writes_state: bool = True) -> torch.Tensor:
+    """A short causal convolution per channel over each sequence's rows, then silu (``activation``).  The convolved
+    channels are columns ``offset .. offset + channels`` of ``x``; ``weight`` [channels, taps] float32 (its last column
+    multiplies the current row), ``bias`` [channels] float32 or None; ``tail`` [slots, taps - 1, channels] float32 holds
+    each sequence's last taps - 1 inputs and, with ``writes_state``, is left at those after this step.  Returns float32
+    [tokens, channels]."""
+    n, taps = x.shape[0], weight.shape[1]
+    if weight.dtype != torch.float32 or tuple(weight.shape) != (channels, taps) or tail.dtype != torch.float32 \
+            or tuple(tail.shape[1:]) != (taps - 1, channels) or (bias is not None and bias.dtype != torch.float32):
+        raise KernelError("causal_conv: weight [channels, taps], bias and tail [slots, taps - 1, channels] are float32")
+    out = torch.empty((n, channels), dtype=torch.float32, device=x.device)
+    _call("state_scan", "fms_causal_conv", _ptr(x) + offset * x.element_size(), _code(x.dtype), x.shape[1], _ptr(weight),
+          _ptr(bias), _ptr(tail), _ptr(batch.token_seq), _ptr(batch.first_row), _ptr(batch.slots), _ptr(out), n,
+          batch.n_seqs, channels, taps, 1 if activation else 0, 1 if writes_state else 0, tail.shape[0], _stream())
+    global launches
+    launches += 1 if writes_state and taps > 1 else 0
+    return out
+
+
+def selective_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                   d_skip: torch.Tensor, state: torch.Tensor, batch, heads: int, vdim: int, n_state: int, groups: int,
+                   writes_state: bool = True) -> torch.Tensor:
+    """Per head, S = exp(-exp(a_log) dt) S + dt B x^T and y = S^T C + d_skip x over each sequence's rows, with
+    dt = softplus(proj[:, dt_offset + head] + dt_bias).  ``xbc`` float32 [tokens, heads * vdim + 2 groups * n_state] =
+    [x | B | C]; ``state`` float32 [slots, heads, vdim, n_state].  Returns y float32 [tokens, heads * vdim]."""
+    n = xbc.shape[0]
+    if xbc.dtype != torch.float32 or state.dtype != torch.float32 or xbc.shape[1] != heads * vdim + 2 * groups * n_state \
+            or tuple(state.shape[1:]) != (heads, vdim, n_state):
+        raise KernelError("selective_scan: xbc float32 [tokens, x | B | C], state float32 [slots, heads, vdim, state]")
+    y = torch.empty((n, heads * vdim), dtype=torch.float32, device=xbc.device)
+    _call("state_scan", "fms_selective_scan", _ptr(xbc), _ptr(proj) + dt_offset * proj.element_size(), _code(proj.dtype),
+          proj.shape[1], _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(y), _ptr(batch.first_row),
+          _ptr(batch.slots), batch.n_seqs, heads, vdim, n_state, groups, 1 if writes_state else 0, state.shape[0],
+          _stream())
+    return y
+
+
+def delta_rule_scan(qkv: torch.Tensor, proj: torch.Tensor, beta_offset: int, a_raw: torch.Tensor, dt_bias: torch.Tensor,
+                    a_log: torch.Tensor, state: torch.Tensor, batch, heads: int, kvheads: int, dim: int, vdim: int,
+                    writes_state: bool = True) -> torch.Tensor:
+    """Per head, S = diag(g) S; u = beta (v - S^T k); S += k u^T; o = S^T q over each sequence's rows.  ``qkv`` float32
+    [tokens, 2 kvheads * dim + heads * vdim] = [q | k | v]; beta = sigmoid(proj[:, beta_offset + head]);
+    g = exp(-exp(a_log[head]) softplus(a_raw + dt_bias)), [heads * dim] a row; ``state`` float32 [slots, heads, vdim, dim].
+    Returns o float32 [tokens, heads * vdim]."""
+    n = qkv.shape[0]
+    if qkv.dtype != torch.float32 or state.dtype != torch.float32 or qkv.shape[1] != 2 * kvheads * dim + heads * vdim \
+            or tuple(state.shape[1:]) != (heads, vdim, dim) or tuple(a_raw.shape) != (n, heads * dim) \
+            or a_raw.dtype != proj.dtype:
+        raise KernelError("delta_rule_scan: qkv float32 [tokens, q | k | v], state float32 [slots, heads, vdim, dim]")
+    o = torch.empty((n, heads * vdim), dtype=torch.float32, device=qkv.device)
+    _call("state_scan", "fms_delta_rule_scan", _ptr(qkv), _ptr(proj) + beta_offset * proj.element_size(),
+          _code(proj.dtype), proj.shape[1], _ptr(a_raw), _ptr(dt_bias), _ptr(a_log), _ptr(state), _ptr(o),
+          _ptr(batch.first_row), _ptr(batch.slots), batch.n_seqs, heads, kvheads, dim, vdim, 1 if writes_state else 0,
+          state.shape[0], _stream())
+    return o
+
+
+GATE_NONE, GATE_SILU_BEFORE, GATE_SIGMOID_AFTER = 0, 1, 2
+
+
+def gated_group_rmsnorm(x: torch.Tensor, gate: Optional[torch.Tensor], gate_offset: int, gate_mode: int,
+                        weight: torch.Tensor, eps: float, group_size: int, out_dtype: torch.dtype,
+                        factor: float = 1.0) -> torch.Tensor:
+    """Rows of ``x`` (float32) cut into groups of ``group_size``, each divided by its root mean square, times
+    ``weight`` (float32; repeated along the row where it is shorter), times ``factor``.  ``gate``: a matrix whose
+    columns from ``gate_offset`` on are the gates' logits: ``GATE_SILU_BEFORE`` multiplies x by silu(gate) before the
+    norm, ``GATE_SIGMOID_AFTER`` the normed and weighted values by sigmoid(gate)."""
+    n, width = x.shape
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or width % weight.shape[0]:
+        raise KernelError("gated_group_rmsnorm: x and weight are float32, the weight's length divides the row's")
+    if gate is not None and gate.dtype != out_dtype:
+        raise KernelError(f"gated_group_rmsnorm: gate {gate.dtype}, compute dtype {out_dtype}")
+    out = torch.empty((n, width), dtype=out_dtype, device=x.device)
+    gate_ptr = None if gate is None else _ptr(gate) + gate_offset * gate.element_size()
+    _call("state_scan", "fms_gated_group_rmsnorm", _ptr(x), gate_ptr, _code(out_dtype), 0 if gate is None else gate.shape[1],
+          int(gate_mode) if gate is not None else GATE_NONE, _ptr(weight), weight.shape[0], float(eps), float(factor),
+          _ptr(out), n, width, int(group_size), _stream())
+    return out
 
 
 # ---- groups of rows, each with a matrix of its own ---------------------------------------------------

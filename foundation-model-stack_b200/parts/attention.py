@@ -20,6 +20,8 @@ from __future__ import annotations
 
 import math
 
+import torch
+
 from ..cache.requests import KVRequest
 from ..config.specs import MixerSpec
 from ..kernels import ops
@@ -67,4 +69,78 @@ class MultiHeadAttention(Part):
                 + ["elementwise", f"attention_hd{self.head_dim}"])
 
 
+class SinkAttention(Part):
+    """``sink_attention``: grouped-query softmax attention over the cache with, each of them optional,
+
+        rotation of only the first ``rot_dims`` values of every head (adjacent pairs; ``position`` gives base and scaling)
+        q and k divided by their root mean square over the head, after the rotation (``qk_norm``, eps ``eps``; no gain)
+        a learned sink per head in the softmax's denominator: p_j = exp(s_j) / (sum_i exp(s_i) + exp(sink_h))   (``sink``)
+        a gate on the heads' results before the output projection: o * sigmoid(Wg h)                            (``gate``)
+        values of another size than keys (``vdim``)
+
+    [Wq; Wk; Wv; Wg] is one fused projection (``in_proj``; bias [bq; bk; bv; 0] where ``bias``).  The cache holds heads
+    of ``pad`` = max(head_dim, vdim) rounded up to 16 values, zeros beyond each one's own size, so that the attention
+    kernels built for one head size serve keys and values alike; q is padded the same way and the padding of the
+    result is dropped by the gate kernel.  ``out_factor`` multiplies the result before the output projection (a mixer
+    that stands beside another one carries its weight there)."""
+
+    def __init__(self, spec: MixerSpec) -> None:
+        super().__init__()
+        o = dict(spec.options)
+        if spec.nheads <= 0 or spec.kvheads <= 0 or spec.nheads % spec.kvheads:
+            raise ValueError(f"nheads {spec.nheads} must be a positive multiple of kvheads {spec.kvheads}")
+        self.nheads, self.kvheads, self.head_dim = spec.nheads, spec.kvheads, spec.head_dim
+        self.vdim = int(o.get("vdim", spec.head_dim))
+        self.pad = (max(self.head_dim, self.vdim) + 15) // 16 * 16
+        if self.head_dim <= 0 or self.vdim <= 0 or self.pad > 256:
+            raise ValueError(f"sink_attention: heads of {self.head_dim} and values of {self.vdim}: up to 256 are supported")
+        self.rot_dims = int(o.get("rot_dims", 0))
+        if self.rot_dims % 2 or not (0 <= self.rot_dims <= self.head_dim):
+            raise ValueError(f"sink_attention: {self.rot_dims} rotated values of {self.head_dim}")
+        self.qk_norm, self.eps = bool(o.get("qk_norm", False)), float(o.get("eps", 1e-6))
+        self.has_sink, self.has_gate = bool(o.get("sink", False)), bool(o.get("gate", False))
+        self.out_factor = float(o.get("out_factor", 1.0))
+        self.scale = 1.0 / math.sqrt(spec.head_dim) if spec.scale is None else float(spec.scale)
+        self.window = int(spec.window)
+        self.position_spec = spec.position
+        self.gate_col = (self.nheads + self.kvheads) * self.head_dim + self.kvheads * self.vdim
+        rows = self.gate_col + (self.nheads * self.vdim if self.has_gate else 0)
+        self.in_proj = self.add("in_proj", Linear(spec.dim, rows, spec.bias))
+        if self.has_sink:
+            self.declare("sink", (self.nheads,), role="vector")
+        self.dense = self.add("dense", Linear(self.nheads * self.vdim, spec.dim, False))
+        self._inv_freq = self._sink = None
+
+    def finalize(self, device, dtype) -> None:
+        super().finalize(device, dtype)
+        if self.rot_dims:
+            from .position import rotary_inverse_frequencies
+
+            # every frequency in float64, rounded to float32 once
+            f = rotary_inverse_frequencies(self.rot_dims, float(self.position_spec.theta), self.position_spec.scaling_dict(),
+                                           dtype=torch.float64)
+            self._inv_freq = f.to(torch.float32).to(device).contiguous()
+        if self.has_sink:
+            self._sink = self.tensor("sink").float().contiguous()
+
+    def cache_request(self):
+        return KVRequest(self.kvheads, self.pad, self.window)
+
+    def heads_out(self, x, batch, cache_view, writes_cache: bool = True):
+        """The gated heads' results [tokens, nheads * vdim], before the output projection."""
+        proj = self.in_proj.forward(x)
+        q = ops.qk_prepare_store(proj, self._inv_freq, self.rot_dims, self.qk_norm, self.eps, batch, cache_view,
+                                 self.nheads, self.kvheads, self.head_dim, self.vdim, self.pad, writes_cache)
+        o = ops.attention(q, batch, cache_view, self.nheads, self.kvheads, self.pad, self.scale, self.window, self._sink)
+        return ops.sigmoid_gate(o, proj if self.has_gate else None, self.gate_col, self.nheads, self.vdim, self.pad,
+                                self.out_factor)
+
+    def forward(self, x, batch, cache_view, writes_cache: bool = True):
+        return self.dense.forward(self.heads_out(x, batch, cache_view, writes_cache))
+
+    def kernel_libraries(self, dtype):
+        return super().kernel_libraries(dtype) + ["elementwise", f"attention_hd{self.pad}"]
+
+
 register_mixer("attention", MultiHeadAttention)
+register_mixer("sink_attention", SinkAttention)

@@ -12,6 +12,9 @@ Interface of a block (what the decoder calls); ``BlockSpec.arrangement`` names t
 
 ``PreNormBlock`` ("pre_norm", fms/models/llama.py:118-167): x += mixer(norm(x)); x += feed_forward(norm(x)).
 
+``PostNormBlock`` ("post_norm"): x = norm1(alpha x + mixer(x)); x = norm2(alpha x + feed_forward(x)); the sublayers
+read the stream itself, and what the block hands on is a ``StreamCopy`` (nothing pending).
+
 ``SandwichBlock`` ("sandwich"): a norm before and after each sublayer, x += post1(mixer(pre1(x)));
 x += post2(feed_forward(pre2(x))).  What it hands on as pending is a ``NormedDelta``: the next norm (this layer's, the
 next layer's or the decoder's last) norms it, adds it and takes its own norm in one kernel.  A layer without a
@@ -21,7 +24,8 @@ from __future__ import annotations
 
 from ..config.specs import BlockSpec
 from .base import Part
-from .norm import NormedDelta
+from ..kernels import ops
+from .norm import NormedDelta, StreamCopy
 from .registry import build_feed_forward, build_mixer, build_norm, register_block
 
 
@@ -73,6 +77,58 @@ class SandwichBlock(Part):
         return NormedDelta(self.feed_forward.forward(h), self.feed_forward_post_norm)
 
 
+class ScaledParts:
+    """What a mixer made of several returns instead of one tensor: [(output, factor), ...], whose weighted sum is the
+    mixer's output.  The norm that follows takes the sum in float32 on its way, so it is never rounded."""
+
+    __slots__ = ("parts",)
+
+    def __init__(self, parts) -> None:
+        self.parts = list(parts)
+
+
+class PostNormBlock(Part):
+    """``post_norm``: the sublayers read the stream itself and the norm follows the sum,
+    x = norm1(alpha x + mixer(x)); x = norm2(alpha x + feed_forward(x)); option ``alpha`` (1 by default).  A layer
+    without a feed-forward ends after its first norm.  The stream stays float32; each norm also leaves it in the
+    compute dtype for the sublayer that reads it next."""
+
+    def __init__(self, spec: BlockSpec) -> None:
+        super().__init__()
+        n_mixer_norm, n_mixer, n_ff_norm, n_ff = spec.names
+        self.alpha = float(dict(spec.options).get("alpha", 1.0))
+        self.mixer = self.add(n_mixer, build_mixer(spec.mixer))
+        self.mixer_norm = self.add(n_mixer_norm, build_norm(spec.mixer_norm))
+        self.feed_forward = None
+        if spec.feed_forward is not None:
+            if spec.feed_forward_norm is None:
+                raise ValueError("a post-norm layer with a feed-forward needs the norm that follows it")
+            self.feed_forward = self.add(n_ff, build_feed_forward(spec.feed_forward))
+            self.feed_forward_norm = self.add(n_ff_norm, build_norm(spec.feed_forward_norm))
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, residual, pending, batch, cache_view, writes_cache, dtype):
+        if isinstance(pending, StreamCopy):
+            h = pending.rows
+        elif pending is None:
+            h = ops.cast_rows(residual, dtype)
+        else:
+            raise ValueError("a post-norm layer follows a layer that left its output pending; only layers whose norms "
+                             "bring the stream up to date may come before it")
+        a = self.mixer.forward(h, batch, cache_view, writes_cache)
+        parts = a.parts if isinstance(a, ScaledParts) else [(a, 1.0)]
+        h = self.mixer_norm.apply_after_sum(residual, self.alpha, parts, dtype)
+        if self.feed_forward is not None:
+            h = self.feed_forward_norm.apply_after_sum(residual, self.alpha, [(self.feed_forward.forward(h), 1.0)], dtype)
+        return StreamCopy(h)
+
+    def kernel_libraries(self, dtype):
+        return super().kernel_libraries(dtype) + ["elementwise"]
+
+
 Block = PreNormBlock  # the name under which earlier callers know it
+register_block("post_norm", PostNormBlock)
 register_block("pre_norm", PreNormBlock)
 register_block("sandwich", SandwichBlock)

@@ -38,21 +38,53 @@ class NormedDelta:
         self.norm = norm
 
 
+class StreamCopy:
+    """What a layer hands on when its own norms have already brought the stream up to date (a layer whose norm follows
+    the sum): nothing is pending; ``rows`` is the stream in the compute dtype (the stream itself where that is
+    float32), so that a next layer that reads the stream need not make that copy again."""
+
+    __slots__ = ("rows",)
+
+    def __init__(self, rows) -> None:
+        self.rows = rows
+
+
 class RMSNorm(Part):
+    """Option ``offset``: the stored weight lies around zero and the gain is offset + weight (taken in float32 once,
+    when the weights are loaded, so that a weight stored in 16 bits loses nothing in the sum)."""
+
     def __init__(self, spec: NormSpec) -> None:
         super().__init__()
         self.dim = spec.dim
         self.eps = float(spec.eps)
+        self.offset = float(dict(spec.options).get("offset", 0.0))
         self.declare("weight", (spec.dim,), role="vector")
+        self._gain = None
+
+    def finalize(self, device, dtype) -> None:
+        super().finalize(device, dtype)
+        if self.offset != 0.0:
+            self._gain = (self.tensor("weight").float() + self.offset).contiguous()
+
+    def gain_vector(self):
+        return self._gain if self._gain is not None else self.tensor("weight")
 
     def gain(self):
         """(vector or None, the one number where there is no vector, eps): what the fused kernel takes."""
-        return self.tensor("weight"), 1.0, self.eps
+        return self.gain_vector(), 1.0, self.eps
 
     def apply(self, residual, delta, out_dtype, rows=None):
+        if isinstance(delta, StreamCopy):
+            delta = None
         if isinstance(delta, NormedDelta):
             return ops.normed_add_rmsnorm(residual, delta.delta, delta.norm.gain(), self.gain(), out_dtype, rows)
-        return ops.add_rmsnorm(residual, delta, self.tensor("weight"), self.eps, out_dtype, rows)
+        return ops.add_rmsnorm(residual, delta, self.gain_vector(), self.eps, out_dtype, rows)
+
+    def apply_after_sum(self, residual, alpha, parts, out_dtype):
+        """residual = norm(alpha * residual + sum of factor * delta over ``parts``), in place; returns the new rows in
+        the compute dtype (the stream itself where that is float32)."""
+        copy = ops.scaled_add_rmsnorm(residual, alpha, parts, self.gain_vector(), self.eps, out_dtype)
+        return residual if copy is None else copy
 
     def kernel_libraries(self, dtype):
         return ["elementwise"]
@@ -75,6 +107,8 @@ class ScalarRMSNorm(Part):
 
     def apply(self, residual, delta, out_dtype, rows=None):
         post = None
+        if isinstance(delta, StreamCopy):
+            delta = None
         if isinstance(delta, NormedDelta):
             delta, post = delta.delta, delta.norm.gain()
         return ops.normed_add_rmsnorm(residual, delta, post, self.gain(), out_dtype, rows)

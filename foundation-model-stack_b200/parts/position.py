@@ -36,8 +36,10 @@ from .base import Part
 from .registry import register_position
 
 
-def rotary_inverse_frequencies(head_dim: int, theta: float, scaling: dict) -> torch.Tensor:
-    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2)[: head_dim // 2].float() / head_dim))
+def rotary_inverse_frequencies(head_dim: int, theta: float, scaling: dict, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``dtype``: what the frequencies are computed in (float32 as the reference does; a caller that wants each
+    frequency rounded once asks for float64 and rounds the result)."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2)[: head_dim // 2].to(dtype) / head_dim))
     kind = scaling.get("rope_type", scaling.get("type", "regular")) if scaling else "regular"
     if kind in ("regular", "default", None):
         return inv

@@ -41,7 +41,8 @@ class TensorLayout:
     def __init__(self, name: str, shape: Sequence[int], init: str) -> None:
         self.name = name
         self.shape = tuple(shape)
-        # "matrix", "embedding", "head": N(0, std)   "gain": 1 + U(-0.1, 0.1)   "zeros"; the reference's own
+        # "matrix", "embedding", "head": N(0, std)   "gain": 1 + U(-0.1, 0.1)   "around_zero": U(-0.1, 0.1)
+        # "taps": N(0, 0.5)   "zeros"; the reference's own
         # initialisation (RandomSource(init="fms")) tells the three kinds of matrices apart
         self.init = init
 
@@ -72,7 +73,7 @@ class RandomSource:
 
     def spec(self, name: str):
         t = self.layout[name]
-        return (self.gain_dtype if t.init == "gain" else self.dtype), t.shape
+        return (self.gain_dtype if t.init in ("gain", "around_zero") else self.dtype), t.shape
 
     def get(self, name: str) -> torch.Tensor:
         t = self.layout[name]
@@ -94,6 +95,12 @@ class RandomSource:
                 return torch.ones(t.shape, dtype=self.gain_dtype, device=self.device)
             x = torch.empty(t.shape, dtype=torch.float32, device=self.device).uniform_(-0.1, 0.1, generator=g)
             return (1.0 + x).to(self.gain_dtype)
+        if t.init == "around_zero":  # weights that are stored as an offset from 1, biases, logarithms of rates
+            x = torch.empty(t.shape, dtype=torch.float32, device=self.device).uniform_(-0.1, 0.1, generator=g)
+            return x.to(self.gain_dtype)
+        if t.init == "taps":  # a short convolution's taps: of the order of 1 / taps each
+            x = torch.empty(t.shape, dtype=torch.float32, device=self.device).normal_(0.0, 0.5, generator=g)
+            return x.to(self.dtype)
         if t.init == "zeros":
             return torch.zeros(t.shape, dtype=self.dtype, device=self.device)
         raise ValueError(f"unknown init {t.init!r}")
