@@ -568,6 +568,118 @@ def run_goletar(args):
 
 
 # --------------------------------------------------------------------------------------------------
+# --compare niletar: the Niletar design beside Llama at equal width, layer for layer
+# --------------------------------------------------------------------------------------------------
+NILETAR_SHAPE = dict(width=4096, vocab=128256, ff=14336, heads=32, kv_heads=8, dim=128, rot_dims=64,
+                     delta_heads=16, delta_kv_heads=16, delta_dim=128, delta_vdim=128, rank=64,
+                     ssm_heads=128, ssm_vdim=64, state=128, groups=8, conv=4)
+
+
+def niletar_layers(kinds, with_mlp=True):
+    from fms_b200.models.niletar import attention_side, delta_side, dense_mlp, mamba2_layer, parallel_layer
+
+    g = NILETAR_SHAPE
+    mlp = dense_mlp(g["ff"]) if with_mlp else None
+    par = lambda: parallel_layer(
+        attention_side(g["heads"], g["kv_heads"], g["dim"], g["dim"], g["rot_dims"], 500000.0, g["dim"] ** -0.5),
+        delta_side(g["delta_heads"], g["delta_kv_heads"], g["delta_dim"], g["delta_vdim"], g["conv"], g["rank"], g["rank"]),
+        0.5, 0.5, mlp)
+    ssm = lambda: mamba2_layer(g["ssm_heads"], g["ssm_vdim"], g["state"], g["groups"], g["groups"], g["conv"], mlp)
+    return [par() if k == "parallel" else ssm() for k in kinds]
+
+
+def niletar_counts(layers, tokens, batch_context, batch):
+    """(flops of a prompt of `tokens`, bytes a decode step of `batch` sequences with `batch_context` cached tokens
+    reads and writes) of the given layers: products, attention over the cache, the two scans (6 flops per state value
+    and token for the state-space scan, 8 for the delta rule: they run in float32 on the CUDA cores), the states of the
+    sequences (read and written once a step)."""
+    g = NILETAR_SHAPE
+    d, flops, moved = g["width"], 0.0, 0.0
+    for layer in layers:
+        m = layer["mixer"]
+        if layer["type"] == "mamba2":
+            h, v, n, gr = m["heads"], m["vdim"], m["state"], m["groups"]
+            inner = h * v
+            w = d * (2 * inner + 2 * gr * n + h) + inner * d
+            flops += 6.0 * tokens * inner * n
+            moved += 2 * 4 * batch * inner * n
+        else:
+            l, r = m["left"], m["right"]
+            w = d * (l["heads"] * l["dim"] + 2 * l["kv_heads"] * l["dim"] + l["heads"] * l["vdim"]) + l["heads"] * l["vdim"] * d
+            flops += 2.0 * tokens * tokens * l["heads"] * l["dim"]  # the causal half of 4 T^2 per head and value
+            moved += 2 * 2 * batch_context * l["kv_heads"] * l["dim"]
+            rk = r.get("decay_rank", 0) + r.get("gate_rank", 0)
+            w += d * (2 * r["kv_heads"] * r["dim"] + r["heads"] * r["vdim"] + r["heads"] + rk) + r["heads"] * r["vdim"] * d
+            w += r["decay_rank"] * r["heads"] * r["dim"] + r["gate_rank"] * r["heads"] * r["vdim"]
+            flops += 8.0 * tokens * r["heads"] * r["dim"] * r["vdim"]
+            moved += 2 * 4 * batch * r["heads"] * r["dim"] * r["vdim"]
+        if layer.get("mlp"):
+            w += 3 * layer["mlp"]["ff"] * d
+        flops += 2.0 * tokens * w
+        moved += 2 * w
+    head = 2 * g["vocab"] * d
+    return flops + head, moved + head
+
+
+class NiletarMeasured(Measured):
+    """A Niletar model of given layers on the device, measured like the Llama one."""
+
+    def __init__(self, layers, room, max_prompt, slots):
+        import torch
+
+        from fms_b200.models.niletar import Niletar, NiletarConfig
+        from fms_b200.weights.sources import RandomSource
+
+        g = NILETAR_SHAPE
+        self.m, self.dtype, self.nlayers, self.itemsize, self.layers = dict(vocab=g["vocab"]), "bf16", len(layers), 2, layers
+        self.model = Niletar(NiletarConfig(vocab=g["vocab"], width=g["width"], postln_alpha=2.0, layers=layers))
+        self.model.load(RandomSource(self.model.checkpoint_layout(), 0, dtype=torch.bfloat16, device="cuda"), "native", "cuda",
+                        torch.bfloat16)
+        self.engine = self.model.new_engine(max_tokens=slots * (max_prompt + 2 * room + 128), max_slots=slots)
+        self.torch = torch
+
+
+def run_niletar(args):
+    """One JSON line: prompts of 512 and 2,048 tokens and decode steps of 1, 8 and 64 sequences, for `--layers` layers
+    (default 4) of the Niletar design at the width of the benchmark's Llama (alternating the parallel mixer and the
+    state-space scan, each with the dense feed-forward of 14,336), for as many Llama-3-8B layers, and for each of
+    Niletar's mixers alone (models of one kind of layer without a feed-forward).  Each figure with its fraction of the
+    measured peak: flops of a prompt over the bf16 product peak, bytes a decode step moves over the copy peak."""
+    pk = peaks()
+    n = args.layers or 4
+    steps, warm = max(16, args.steps // 2), max(3, args.warmup // 2)
+    room = warm + 3 * steps + 8
+    lengths = {1: [1024], 8: [1024] * 8, 64: [1024] * 64}
+    out = {"compare": "niletar", "layers": n, "shape": NILETAR_SHAPE, "peaks": pk, "steps": steps, "warmup": warm, "models": {}}
+
+    def measure(run, name, flops_bytes):
+        row = {}
+        for tokens in (512, 2048):
+            ms = run.prefill(tokens, 3)
+            row[f"prefill_{tokens}"] = {"ms": round(ms, 3), "tok_s": round(tokens / (ms / 1e3), 1),
+                                        "frac_of_bf16_peak": round(flops_bytes(tokens, 0, 0)[0] / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4)}
+        for b in (1, 8, 64):
+            v, ms, ctx, _, _ = run.device_decode(b, steps, warm, lengths[b], regions=3)
+            row[f"decode_b{b}"] = {"ms": round(ms, 4), "tok_s": round(v, 1),
+                                   "frac_of_copy_peak": round(flops_bytes(0, ctx, b)[1] / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+        out["models"][name] = row
+        run.close()
+
+    kinds = ["parallel" if i % 2 == 0 else "mamba2" for i in range(n)]
+    variants = [("niletar", niletar_layers(kinds)), ("parallel_only", niletar_layers(["parallel"] * n, False)),
+                ("mamba2_only", niletar_layers(["mamba2"] * n, False))]
+    if args.only:
+        variants = [v for v in variants if v[0] == args.only]
+    for name, layers in variants:
+        measure(NiletarMeasured(layers, room, 2048, 64), name,
+                lambda tokens, ctx, b, layers=layers: niletar_counts(layers, tokens, ctx, b))
+    if not args.only or args.only == "llama":
+        llama = Measured(MODEL, "bf16", n, room, 2048, slots=64)
+        measure(llama, "llama", lambda tokens, ctx, b: (prefill_flops(n, tokens), decode_bytes(n, ctx)))
+    print(json.dumps(out))
+
+
+# --------------------------------------------------------------------------------------------------
 # the reference, unmodified, through its own public API
 # --------------------------------------------------------------------------------------------------
 def run_reference(args):
@@ -665,9 +777,10 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: the prompt's length")
     ap.add_argument("--points", choices=["default", "main", "long"], default="default",
                     help="main: without the further configurations; long: also decode at batch 64 with 8k contexts")
-    ap.add_argument("--compare", choices=["", "goletar"], default="",
+    ap.add_argument("--compare", choices=["", "goletar", "niletar"], default="",
                     help="goletar: the Goletar design beside as many Llama layers of equal width (--layers, default 4; "
-                    "--only goletar|mingru_only|latent_attention_only|mingru_with_experts|llama for one of them)")
+                    "--only goletar|mingru_only|latent_attention_only|mingru_with_experts|llama for one of them); "
+                    "niletar: the Niletar design likewise (--only niletar|parallel_only|mamba2_only|llama)")
     args = ap.parse_args()
     choose_model(args.model)
     if args.gpus != 1:
@@ -676,6 +789,8 @@ def main():
         sys.exit(2)
     if args.compare == "goletar":
         run_goletar(args)
+    elif args.compare == "niletar":
+        run_niletar(args)
     elif args.impl == "reference":
         run_reference(args)
     elif args.only in ("gemm_rows", "attention_prefill", "attention_decode"):
