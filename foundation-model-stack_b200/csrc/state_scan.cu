@@ -23,30 +23,23 @@
 // is declared __restrict__, and what the kernel right before wrote is read after griddepcontrol.wait.
 namespace {
 constexpr int CH = 16;      // tokens brought into shared memory at a time
-constexpr int PARTS = 4;    // threads that share a value column
-constexpr int VB = 32;      // value columns of a block (VB * PARTS = 128 threads)
+constexpr int PARTS = 8;    // threads that share a group of value columns
 constexpr int MAX_TAPS = 16;
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
-__device__ __forceinline__ float quad_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 1);
-  v += __shfl_xor_sync(0xffffffffu, v, 2);
-  return v;
-}
 
 // ---- causal convolution ------------------------------------------------------------------------------
-// x: rows of `stride` values (the convolved channels are its first `channels` from the pointer on); one thread per
-// (row, channel)
+// x: rows of `stride` values (the convolved channels are its first `channels` from the pointer on); a block per
+// (row, run of 256 channels)
 template <typename T>
 __global__ void causal_conv_kernel(const T* x, int stride, const float* w, const float* bias, const float* tail,
                                    const int* token_seq, const int* first_row, const int* slots, float* out,
                                    int n_tokens, int channels, int taps, int act, int n_seqs, int n_slots) {
   pdl_launch_dependents();
   pdl_wait();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)n_tokens * channels) return;
-  const int t = (int)(i / channels), c = (int)(i - (size_t)t * channels);
+  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
   const int seq = token_seq[t];
   if (!FMS_IN(seq, n_seqs)) return;
   const int local = t - first_row[seq];  // the row's place among its sequence's rows of this step
@@ -60,7 +53,7 @@ __global__ void causal_conv_kernel(const T* x, int stride, const float* w, const
                                   : tl[(size_t)(taps - 1 + local - back) * channels + c];
     acc = fmaf(w[(size_t)c * taps + j], v, acc);
   }
-  out[i] = act ? acc * sigmoid_f(acc) : acc;
+  out[(size_t)t * channels + c] = act ? acc * sigmoid_f(acc) : acc;
 }
 
 // the tail after the step: the last taps - 1 inputs of (old tail, the step's rows); one thread per (sequence, channel)
@@ -89,176 +82,340 @@ __global__ void conv_tail_kernel(const T* x, int stride, float* tail, const int*
   }
 }
 
+// ---- the two scans ------------------------------------------------------------------------------------
+// Both walk a sequence's tokens in order with the state in registers.  A block of 128 threads owns (sequence, head,
+// run of VB = 16 * VP value columns); a thread owns VP columns and NP consecutive state rows of each, and the eight
+// threads (PARTS) that share a column group add their sums by shuffles, so a column's sum runs over its rows in the
+// same order whatever VP is, whatever else is in the batch and however the prompt was cut.  The tokens' vectors
+// come through shared memory CH tokens at a time by cp.async into two stages: the next chunk is on its way while this
+// one is walked.  Rows of shared memory are padded to PARTS * NP values with zeros, so the inner loops need no bounds.
+constexpr int GROUPS = 16;  // column groups of a block (GROUPS * PARTS = 128 threads)
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// rows of `count` floats from global rows (stride src_stride) into shared rows (stride dst_stride), `rows` of them;
+// 16 bytes a copy where `vec` says that every row's start and length allow it
+__device__ __forceinline__ void stage_rows(float* dst, int dst_stride, const float* src, size_t src_stride, int rows,
+                                           int count, bool vec) {
+  if (vec) {
+    const int per = count >> 2;
+    for (int i = threadIdx.x; i < rows * per; i += blockDim.x) {
+      const int r = i / per, c = (i - r * per) << 2;
+      cp_async16(dst + r * dst_stride + c, src + r * src_stride + c);
+    }
+  } else {
+    for (int i = threadIdx.x; i < rows * count; i += blockDim.x) {
+      const int r = i / count, c = i - r * count;
+      cp_async4(dst + r * dst_stride + c, src + r * src_stride + c);
+    }
+  }
+}
+
+// A row of shared memory holds PARTS runs of NP values, one per thread of a column group.  From NP = 8 on the runs lie
+// NP + 4 values apart, so that the eight 16-byte loads of a group's threads fall into different banks.
+template <int NP> struct RowLayout {
+  static constexpr int RUN = NP >= 8 ? NP + 4 : NP;
+  static constexpr int ROW = PARTS * RUN;
+  __device__ static __forceinline__ int at(int n) { return (n / NP) * RUN + (n % NP); }
+};
+template <int NP> __device__ __forceinline__ void load_run(const float* p, float (&r)[NP]) {
+  if constexpr (NP % 4 == 0) {
+#pragma unroll
+    for (int j = 0; j < NP; j += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(p + j);
+      r[j] = v.x; r[j + 1] = v.y; r[j + 2] = v.z; r[j + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < NP; ++j) r[j] = p[j];
+  }
+}
+// `count` floats of each of `rows` global rows into shared rows of the padded layout
+template <int NP>
+__device__ __forceinline__ void stage_runs(float* dst, const float* src, size_t src_stride, int rows, int count, bool vec) {
+  using L = RowLayout<NP>;
+  if (vec) {
+    const int per = count >> 2;
+    for (int i = threadIdx.x; i < rows * per; i += blockDim.x) {
+      const int r = i / per, c = (i - r * per) << 2;
+      cp_async16(dst + r * L::ROW + L::at(c), src + r * src_stride + c);
+    }
+  } else {
+    for (int i = threadIdx.x; i < rows * count; i += blockDim.x) {
+      const int r = i / count, c = i - r * count;
+      cp_async4(dst + r * L::ROW + L::at(c), src + r * src_stride + c);
+    }
+  }
+}
+
+__device__ __forceinline__ float octet_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
+
 // ---- selective state-space scan ----------------------------------------------------------------------
 // xbc [tokens, inner + 2 groups * N] float32 (after the convolution): x | B | C;  dt_raw: column `head` of rows of
-// `dt_stride` values;  y [tokens, inner] float32.  NP: state rows a thread holds (N <= PARTS * NP).
-template <typename T, int NP>
-__global__ void selective_scan_kernel(const float* xbc, const T* dt_raw, int dt_stride, const float* dt_bias,
-                                      const float* a_log, const float* d_skip, float* state, float* y,
-                                      const int* first_row, const int* slots, int heads, int vdim, int n_state,
-                                      int groups, int write_state, int n_slots) {
-  extern __shared__ float smem[];
+// `dt_stride` values (bfloat16 or float32);  y [tokens, inner] float32.
+template <int NP, int VP>
+__global__ void __launch_bounds__(128) selective_scan_kernel(const float* xbc, const void* dt_raw, int dt_is_bf16,
+                                                             int dt_stride, const float* dt_bias, const float* a_log,
+                                                             const float* d_skip, float* state, float* y,
+                                                             const int* first_row, const int* slots, int heads, int vdim,
+                                                             int n_state, int groups, int write_state, int n_slots,
+                                                             int vec_bc, int vec_x) {
+  constexpr int NPAD = RowLayout<NP>::ROW, RUN = RowLayout<NP>::RUN, VB = GROUPS * VP;
+  extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
   const int seq = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * VB;
-  const int tid = threadIdx.x, part = tid % PARTS, vl = tid / PARTS, v = v0 + vl;
-  const bool v_ok = v < vdim;
+  const int tid = threadIdx.x, part = tid % PARTS, grp = tid / PARTS;
   const int slot = __ldcg(slots + seq);
   if (!FMS_IN(slot, n_slots)) return;
   const int lo = first_row[seq], hi = first_row[seq + 1];
   const int inner = heads * vdim, row_w = inner + 2 * groups * n_state;
   const int group = head / (heads / groups);
-  float* sB = smem;                      // [CH][n_state]
-  float* sC = sB + CH * n_state;         // [CH][n_state]
-  float* sx = sC + CH * n_state;         // [CH][VB]
-  float* sdt = sx + CH * VB;             // [CH]
-  float* sdec = sdt + CH;                // [CH]
+  constexpr int STAGE = CH * (2 * NPAD + VB);
+  float* sdt = smem + 2 * STAGE;  // [CH]
+  float* sdec = sdt + CH;         // [CH]
+  const int cols = min(VB, vdim - v0);  // value columns this block really has
+  if (n_state != PARTS * NP || cols != VB)
+    for (int i = tid; i < 2 * STAGE; i += blockDim.x) smem[i] = 0.f;  // the padding stays zero from here on
   const float A = expf(a_log[head]), D = d_skip[head], bias = dt_bias[head];
-  float s[NP];
-  float* st = state + (((size_t)slot * heads + head) * vdim + (v_ok ? v : 0)) * n_state;
+  float s[VP][NP];
 #pragma unroll
-  for (int j = 0; j < NP; ++j) {
-    const int n = j * PARTS + part;
-    s[j] = (v_ok && n < n_state) ? st[n] : 0.f;
+  for (int i = 0; i < VP; ++i) {
+    const int v = v0 + grp * VP + i;
+    const float* st = state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * n_state;
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      const int n = part * NP + j;
+      s[i][j] = (v < vdim && n < n_state) ? st[n] : 0.f;
+    }
   }
-  for (int c0 = lo; c0 < hi; c0 += CH) {
+  __syncthreads();
+  auto issue = [&](int c0, int stage) {
     const int cn = min(CH, hi - c0);
-    __syncthreads();
-    for (int i = tid; i < cn * n_state; i += blockDim.x) {
-      const int t = i / n_state, n = i - t * n_state;
-      const float* r = xbc + (size_t)(c0 + t) * row_w + inner + (size_t)group * n_state + n;
-      sB[i] = r[0];
-      sC[i] = r[(size_t)groups * n_state];
-    }
-    for (int i = tid; i < cn * VB; i += blockDim.x) {
-      const int t = i / VB, e = i - t * VB;
-      sx[i] = v0 + e < vdim ? xbc[(size_t)(c0 + t) * row_w + (size_t)head * vdim + v0 + e] : 0.f;
-    }
+    float* base = smem + stage * STAGE;
+    const float* src = xbc + (size_t)c0 * row_w;
+    stage_runs<NP>(base, src + inner + (size_t)group * n_state, row_w, cn, n_state, vec_bc);
+    stage_runs<NP>(base + CH * NPAD, src + inner + (size_t)(groups + group) * n_state, row_w, cn, n_state, vec_bc);
+    stage_rows(base + 2 * CH * NPAD, VB, src + (size_t)head * vdim + v0, row_w, cn, cols, vec_x);
+    cp_async_commit();
+  };
+  if (lo < hi) issue(lo, 0);
+  int stage = 0;
+  for (int c0 = lo; c0 < hi; c0 += CH, stage ^= 1) {
+    const int cn = min(CH, hi - c0);
+    const bool more = c0 + CH < hi;
+    if (more) issue(c0 + CH, stage ^ 1);
     if (tid < cn) {
-      const float dt = softplus_f(to_f32(dt_raw[(size_t)(c0 + tid) * dt_stride + head]) + bias);
+      const size_t at = (size_t)(c0 + tid) * dt_stride + head;
+      const float raw = dt_is_bf16 ? __bfloat162float(((const __nv_bfloat16*)dt_raw)[at]) : ((const float*)dt_raw)[at];
+      const float dt = softplus_f(raw + bias);
       sdt[tid] = dt;
       sdec[tid] = expf(-A * dt);
     }
+    if (more) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
+    const float* sB = smem + stage * STAGE;
+    const float* sC = sB + CH * NPAD;
+    const float* sx = sC + CH * NPAD;
     for (int t = 0; t < cn; ++t) {
-      const float xv = sx[t * VB + vl], dtx = sdt[t] * xv, dec = sdec[t];
-      const float* b = sB + t * n_state + part;
-      const float* c = sC + t * n_state + part;
-      float acc = 0.f;
+      const float dec = sdec[t], dt = sdt[t];
+      float xv[VP], dtx[VP], acc[VP];
+#pragma unroll
+      for (int i = 0; i < VP; ++i) {
+        xv[i] = sx[t * VB + grp * VP + i];
+        dtx[i] = dt * xv[i];
+        acc[i] = 0.f;
+      }
+      float b[NP], c[NP];
+      load_run<NP>(sB + t * NPAD + part * RUN, b);
+      load_run<NP>(sC + t * NPAD + part * RUN, c);
 #pragma unroll
       for (int j = 0; j < NP; ++j) {
-        if (j * PARTS + part < n_state) {
-          s[j] = fmaf(dec, s[j], dtx * b[j * PARTS]);
-          acc = fmaf(s[j], c[j * PARTS], acc);
+        const float bj = b[j], cj = c[j];
+#pragma unroll
+        for (int i = 0; i < VP; ++i) {
+          s[i][j] = fmaf(dec, s[i][j], dtx[i] * bj);
+          acc[i] = fmaf(s[i][j], cj, acc[i]);
         }
       }
-      acc = quad_sum(acc);
-      if (part == 0 && v_ok) y[(size_t)(c0 + t) * inner + (size_t)head * vdim + v] = fmaf(D, xv, acc);
-    }
-  }
-  if (write_state && v_ok) {
 #pragma unroll
-    for (int j = 0; j < NP; ++j) {
-      const int n = j * PARTS + part;
-      if (n < n_state) st[n] = s[j];
+      for (int i = 0; i < VP; ++i) {
+        acc[i] = octet_sum(acc[i]);
+        const int v = v0 + grp * VP + i;
+        if (part == i && v < vdim) y[(size_t)(c0 + t) * inner + (size_t)head * vdim + v] = fmaf(D, xv[i], acc[i]);
+      }
+    }
+    __syncthreads();  // this stage and sdt are free again
+  }
+  if (write_state) {
+#pragma unroll
+    for (int i = 0; i < VP; ++i) {
+      const int v = v0 + grp * VP + i;
+      if (v >= vdim) continue;
+      float* st = state + (((size_t)slot * heads + head) * vdim + v) * n_state;
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const int n = part * NP + j;
+        if (n < n_state) st[n] = s[i][j];
+      }
     }
   }
 }
 
 // ---- gated delta rule --------------------------------------------------------------------------------
-// qkv [tokens, 2 kvheads * dim + heads * vdim] float32 (after the convolution): q | k | v;  beta_raw: column `head`
-// of rows of `beta_stride` values;  a_raw [tokens, heads * dim] (the decay's projection);  o [tokens, heads * vdim]
-template <typename T, int NP>
-__global__ void delta_rule_scan_kernel(const float* qkv, const T* beta_raw, int beta_stride, const T* a_raw,
-                                       const float* dt_bias, const float* a_log, float* state, float* o,
-                                       const int* first_row, const int* slots, int heads, int kvheads, int dim, int vdim,
-                                       int write_state, int n_slots) {
-  extern __shared__ float smem[];
+// What enters the recurrence, made ready for every token at once (one block per token, a warp per head):
+//   qkv [tokens, 2 kvheads * dim + heads * vdim] float32 (after the convolution): q | k | v;  q and k of every key head
+//   become unit vectors in place, x / sqrt(sum(x^2) + 1e-6), q also times dim^-1/2
+//   decay[t, h, n] = exp(-exp(a_log[h]) * softplus(a_raw[t, h, n] + dt_bias[h, n]));  beta[t, h] = sigmoid(beta_raw[t, h])
+template <typename T>
+__global__ void delta_prepare_kernel(float* qkv, const T* a_raw, const T* beta_raw, int beta_stride, const float* dt_bias,
+                                     const float* a_log, float* decay, float* beta, int heads, int kvheads, int dim,
+                                     int vdim) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int row_w = 2 * kvheads * dim + heads * vdim;
+  const float q_scale = 1.f / sqrtf((float)dim);
+  for (int item = warp; item < 2 * kvheads + heads; item += nwarps) {
+    if (item < 2 * kvheads) {  // q heads, then k heads
+      float* x = qkv + (size_t)t * row_w + (size_t)item * dim;
+      float ss = 0.f;
+      for (int n = lane; n < dim; n += 32) ss = fmaf(x[n], x[n], ss);
+      const float inv = (item < kvheads ? q_scale : 1.f) / sqrtf(warp_sum(ss) + 1e-6f);
+      for (int n = lane; n < dim; n += 32) x[n] *= inv;
+    } else {
+      const int h = item - 2 * kvheads;
+      const float A = expf(a_log[h]);
+      const size_t at = ((size_t)t * heads + h) * dim;
+      for (int n = lane; n < dim; n += 32)
+        decay[at + n] = expf(-A * softplus_f(to_f32(a_raw[at + n]) + dt_bias[(size_t)h * dim + n]));
+      if (lane == 0) beta[(size_t)t * heads + h] = sigmoid_f(to_f32(beta_raw[(size_t)t * beta_stride + h]));
+    }
+  }
+}
+
+// qkv as delta_prepare_kernel left it; decay [tokens, heads * dim], beta [tokens, heads]; o [tokens, heads * vdim]
+template <int NP, int VP>
+__global__ void __launch_bounds__(128) delta_rule_scan_kernel(const float* qkv, const float* decay, const float* beta,
+                                                              float* state, float* o, const int* first_row,
+                                                              const int* slots, int heads, int kvheads, int dim, int vdim,
+                                                              int write_state, int n_slots, int vec_qk, int vec_g,
+                                                              int vec_v) {
+  constexpr int NPAD = RowLayout<NP>::ROW, RUN = RowLayout<NP>::RUN, VB = GROUPS * VP;
+  extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
   const int seq = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * VB;
-  const int tid = threadIdx.x, part = tid % PARTS, vl = tid / PARTS, v = v0 + vl;
-  const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  const bool v_ok = v < vdim;
+  const int tid = threadIdx.x, part = tid % PARTS, grp = tid / PARTS;
   const int slot = __ldcg(slots + seq);
   if (!FMS_IN(slot, n_slots)) return;
   const int lo = first_row[seq], hi = first_row[seq + 1];
   const int kvh = head / (heads / kvheads);
   const int row_w = 2 * kvheads * dim + heads * vdim;
-  float* sq = smem;               // [CH][dim]
-  float* sk = sq + CH * dim;      // [CH][dim]
-  float* sg = sk + CH * dim;      // [CH][dim]
-  float* sv = sg + CH * dim;      // [CH][VB]
-  float* sbeta = sv + CH * VB;    // [CH]
-  const float A = expf(a_log[head]);
-  const float q_scale = 1.f / sqrtf((float)dim);
-  float s[NP];
-  float* st = state + (((size_t)slot * heads + head) * vdim + (v_ok ? v : 0)) * dim;
+  constexpr int STAGE = CH * (3 * NPAD + VB + 1);
+  const int cols = min(VB, vdim - v0);
+  if (dim != PARTS * NP || cols != VB)
+    for (int i = tid; i < 2 * STAGE; i += blockDim.x) smem[i] = 0.f;  // the padding stays zero from here on
+  float s[VP][NP];
 #pragma unroll
-  for (int j = 0; j < NP; ++j) {
-    const int n = j * PARTS + part;
-    s[j] = (v_ok && n < dim) ? st[n] : 0.f;
-  }
-  for (int c0 = lo; c0 < hi; c0 += CH) {
-    const int cn = min(CH, hi - c0);
-    __syncthreads();
-    for (int i = tid; i < cn * dim; i += blockDim.x) {
-      const int t = i / dim, n = i - t * dim;
-      const float* r = qkv + (size_t)(c0 + t) * row_w + (size_t)kvh * dim + n;
-      sq[i] = r[0];
-      sk[i] = r[(size_t)kvheads * dim];
-      const float a = to_f32(a_raw[(size_t)(c0 + t) * heads * dim + (size_t)head * dim + n]) + dt_bias[(size_t)head * dim + n];
-      sg[i] = expf(-A * softplus_f(a));
-    }
-    for (int i = tid; i < cn * VB; i += blockDim.x) {
-      const int t = i / VB, e = i - t * VB;
-      sv[i] = v0 + e < vdim ? qkv[(size_t)(c0 + t) * row_w + 2 * (size_t)kvheads * dim + (size_t)head * vdim + v0 + e] : 0.f;
-    }
-    if (tid < cn) sbeta[tid] = sigmoid_f(to_f32(beta_raw[(size_t)(c0 + tid) * beta_stride + head]));
-    __syncthreads();
-    for (int t = warp; t < cn; t += nwarps) {  // unit vectors: a warp per token
-      float qq = 0.f, kk = 0.f;
-      for (int n = lane; n < dim; n += 32) {
-        qq = fmaf(sq[t * dim + n], sq[t * dim + n], qq);
-        kk = fmaf(sk[t * dim + n], sk[t * dim + n], kk);
-      }
-      const float qi = q_scale / sqrtf(warp_sum(qq) + 1e-6f), ki = 1.f / sqrtf(warp_sum(kk) + 1e-6f);
-      for (int n = lane; n < dim; n += 32) {
-        sq[t * dim + n] *= qi;
-        sk[t * dim + n] *= ki;
-      }
-    }
-    __syncthreads();
-    for (int t = 0; t < cn; ++t) {
-      const float* q = sq + t * dim + part;
-      const float* k = sk + t * dim + part;
-      const float* g = sg + t * dim + part;
-      float acc = 0.f;
-#pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        if (j * PARTS + part < dim) {
-          s[j] *= g[j * PARTS];
-          acc = fmaf(s[j], k[j * PARTS], acc);
-        }
-      }
-      const float u = sbeta[t] * (sv[t * VB + vl] - quad_sum(acc));
-      float out = 0.f;
-#pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        if (j * PARTS + part < dim) {
-          s[j] = fmaf(k[j * PARTS], u, s[j]);
-          out = fmaf(s[j], q[j * PARTS], out);
-        }
-      }
-      out = quad_sum(out);
-      if (part == 0 && v_ok) o[(size_t)(c0 + t) * heads * vdim + (size_t)head * vdim + v] = out;
-    }
-  }
-  if (write_state && v_ok) {
+  for (int i = 0; i < VP; ++i) {
+    const int v = v0 + grp * VP + i;
+    const float* st = state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * dim;
 #pragma unroll
     for (int j = 0; j < NP; ++j) {
-      const int n = j * PARTS + part;
-      if (n < dim) st[n] = s[j];
+      const int n = part * NP + j;
+      s[i][j] = (v < vdim && n < dim) ? st[n] : 0.f;
+    }
+  }
+  __syncthreads();
+  auto issue = [&](int c0, int stage) {
+    const int cn = min(CH, hi - c0);
+    float* base = smem + stage * STAGE;
+    const float* src = qkv + (size_t)c0 * row_w;
+    stage_runs<NP>(base, src + (size_t)kvh * dim, row_w, cn, dim, vec_qk);
+    stage_runs<NP>(base + CH * NPAD, src + (size_t)(kvheads + kvh) * dim, row_w, cn, dim, vec_qk);
+    stage_runs<NP>(base + 2 * CH * NPAD, decay + ((size_t)c0 * heads + head) * dim, (size_t)heads * dim, cn, dim, vec_g);
+    stage_rows(base + 3 * CH * NPAD, VB, src + 2 * (size_t)kvheads * dim + (size_t)head * vdim + v0, row_w, cn, cols, vec_v);
+    stage_rows(base + 3 * CH * NPAD + CH * VB, 1, beta + (size_t)c0 * heads + head, heads, cn, 1, false);
+    cp_async_commit();
+  };
+  if (lo < hi) issue(lo, 0);
+  int stage = 0;
+  for (int c0 = lo; c0 < hi; c0 += CH, stage ^= 1) {
+    const int cn = min(CH, hi - c0);
+    const bool more = c0 + CH < hi;
+    if (more) issue(c0 + CH, stage ^ 1);
+    if (more) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();
+    const float* sq = smem + stage * STAGE;
+    const float* sk = sq + CH * NPAD;
+    const float* sg = sk + CH * NPAD;
+    const float* sv = sg + CH * NPAD;
+    const float* sbeta = sv + CH * VB;
+    for (int t = 0; t < cn; ++t) {
+      float q[NP], k[NP], g[NP];
+      load_run<NP>(sk + t * NPAD + part * RUN, k);
+      load_run<NP>(sg + t * NPAD + part * RUN, g);
+      load_run<NP>(sq + t * NPAD + part * RUN, q);
+      float acc[VP], u[VP];
+#pragma unroll
+      for (int i = 0; i < VP; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const float gj = g[j], kj = k[j];
+#pragma unroll
+        for (int i = 0; i < VP; ++i) {
+          s[i][j] *= gj;
+          acc[i] = fmaf(s[i][j], kj, acc[i]);
+        }
+      }
+      const float bt = sbeta[t];
+#pragma unroll
+      for (int i = 0; i < VP; ++i) {
+        u[i] = bt * (sv[t * VB + grp * VP + i] - octet_sum(acc[i]));
+        acc[i] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const float kj = k[j], qj = q[j];
+#pragma unroll
+        for (int i = 0; i < VP; ++i) {
+          s[i][j] = fmaf(kj, u[i], s[i][j]);
+          acc[i] = fmaf(s[i][j], qj, acc[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < VP; ++i) {
+        acc[i] = octet_sum(acc[i]);
+        const int v = v0 + grp * VP + i;
+        if (part == i && v < vdim) o[(size_t)(c0 + t) * heads * vdim + (size_t)head * vdim + v] = acc[i];
+      }
+    }
+    __syncthreads();  // this stage is free again
+  }
+  if (write_state) {
+#pragma unroll
+    for (int i = 0; i < VP; ++i) {
+      const int v = v0 + grp * VP + i;
+      if (v >= vdim) continue;
+      float* st = state + (((size_t)slot * heads + head) * vdim + v) * dim;
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const int n = part * NP + j;
+        if (n < dim) st[n] = s[i][j];
+      }
     }
   }
 }
@@ -312,9 +469,8 @@ FMS_API int fms_causal_conv(const void* x, int dtype, int stride, const float* w
                             cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (taps < 1 || taps > MAX_TAPS) return fms_fail("causal_conv: %d taps (1..%d)", taps, MAX_TAPS);
-  const size_t total = (size_t)n_tokens * channels;
   FMS_DISPATCH_DTYPE(dtype, T, {
-    fms_launch(causal_conv_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const T*)x, stride, w,
+    fms_launch(causal_conv_kernel<T>, dim3(n_tokens, (channels + 255) / 256), dim3(256), 0, stream, (const T*)x, stride, w,
                bias, (const float*)tail, token_seq, first_row, slots, out, n_tokens, channels, taps, act, n_seqs, n_slots);
     if (write_state && taps > 1)
       fms_launch(conv_tail_kernel<T>, dim3((channels + 127) / 128, n_seqs), dim3(128), 0, stream, (const T*)x, stride, tail,
@@ -323,56 +479,82 @@ FMS_API int fms_causal_conv(const void* x, int dtype, int stride, const float* w
   return fms_launch_status("causal_conv");
 }
 
+// how many value columns a thread takes: as many as leave every multiprocessor four blocks, whose warps hide one
+// another's latencies (the sums do not depend on it)
+static int columns_per_thread(int n_seqs, int heads, int vdim, int np) {
+  const int most = np >= 32 ? 2 : 4;
+  for (int vp = most; vp > 1; vp >>= 1)
+    if ((long)n_seqs * heads * ((vdim + GROUPS * vp - 1) / (GROUPS * vp)) >= 592 && vdim >= GROUPS * vp) return vp;
+  return 1;
+}
+static bool rows_allow_16(const void* base, long offset, long stride, int count) {
+  return ((uintptr_t)base % 16 == 0) && offset % 4 == 0 && stride % 4 == 0 && count % 4 == 0;
+}
+
+#define FMS_SCAN_SHAPES(LAUNCH)                                   \
+  do {                                                            \
+    if (np <= 2) { if (vp == 4) LAUNCH(2, 4); else if (vp == 2) LAUNCH(2, 2); else LAUNCH(2, 1); }            \
+    else if (np <= 4) { if (vp == 4) LAUNCH(4, 4); else if (vp == 2) LAUNCH(4, 2); else LAUNCH(4, 1); }       \
+    else if (np <= 8) { if (vp == 4) LAUNCH(8, 4); else if (vp == 2) LAUNCH(8, 2); else LAUNCH(8, 1); }       \
+    else if (np <= 16) { if (vp == 4) LAUNCH(16, 4); else if (vp == 2) LAUNCH(16, 2); else LAUNCH(16, 1); }   \
+    else { if (vp == 2) LAUNCH(32, 2); else LAUNCH(32, 1); }                                                  \
+  } while (0)
+
 FMS_API int fms_selective_scan(const float* xbc, const void* dt_raw, int dtype, int dt_stride, const float* dt_bias,
                                const float* a_log, const float* d_skip, float* state, float* y, const int* first_row,
                                const int* slots, int n_seqs, int heads, int vdim, int n_state, int groups,
                                int write_state, int n_slots, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
-  if (heads <= 0 || groups <= 0 || heads % groups || n_state <= 0 || n_state > PARTS * 64 || vdim <= 0)
-    return fms_fail("selective_scan: %d heads, %d groups, state %d (up to %d), vdim %d", heads, groups, n_state, PARTS * 64, vdim);
-  const dim3 grid(n_seqs, heads, (vdim + VB - 1) / VB), block(VB * PARTS);
-  const size_t smem = ((size_t)2 * CH * n_state + CH * VB + 2 * CH) * sizeof(float);
+  if (heads <= 0 || groups <= 0 || heads % groups || n_state <= 0 || n_state > PARTS * 32 || vdim <= 0)
+    return fms_fail("selective_scan: %d heads, %d groups, state %d (up to %d), vdim %d", heads, groups, n_state, PARTS * 32, vdim);
+  if (dtype != FMS_F32 && dtype != FMS_BF16) return fms_fail("selective_scan: dtype code %d", dtype);
   const int np = (n_state + PARTS - 1) / PARTS;
-#define FMS_SCAN(NP)                                                                                                    \
+  const int vp = columns_per_thread(n_seqs, heads, vdim, np);
+  const long row_w = (long)heads * vdim + 2L * groups * n_state;
+  const int vec_bc = rows_allow_16(xbc, (long)heads * vdim, row_w, n_state) && n_state % 4 == 0;
+  const int vec_x = rows_allow_16(xbc, 0, row_w, vdim) && (GROUPS * vp) % 4 == 0 && vdim % (GROUPS * vp) == 0;
+  const dim3 grid(n_seqs, heads, (vdim + GROUPS * vp - 1) / (GROUPS * vp)), block(GROUPS * PARTS);
+#define FMS_LAUNCH(NP, VP)                                                                                              \
   do {                                                                                                                  \
-    cudaFuncSetAttribute(selective_scan_kernel<T, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
-    fms_launch(selective_scan_kernel<T, NP>, grid, block, smem, stream, xbc, (const T*)dt_raw, dt_stride, dt_bias, a_log, \
-               d_skip, state, y, first_row, slots, heads, vdim, n_state, groups, write_state, n_slots);                  \
+    const size_t smem = ((size_t)2 * CH * (2 * RowLayout<NP>::ROW + GROUPS * VP) + 2 * CH) * sizeof(float);                      \
+    cudaFuncSetAttribute(selective_scan_kernel<NP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+    fms_launch(selective_scan_kernel<NP, VP>, grid, block, smem, stream, xbc, dt_raw, dtype == FMS_BF16 ? 1 : 0, dt_stride, \
+               dt_bias, a_log, d_skip, state, y, first_row, slots, heads, vdim, n_state, groups, write_state, n_slots,   \
+               vec_bc, vec_x);                                                                                           \
   } while (0)
-  FMS_DISPATCH_DTYPE(dtype, T, {
-    if (np <= 8) FMS_SCAN(8);
-    else if (np <= 16) FMS_SCAN(16);
-    else if (np <= 32) FMS_SCAN(32);
-    else FMS_SCAN(64);
-  });
-#undef FMS_SCAN
+  FMS_SCAN_SHAPES(FMS_LAUNCH);
+#undef FMS_LAUNCH
   return fms_launch_status("selective_scan");
 }
 
-FMS_API int fms_delta_rule_scan(const float* qkv, const void* beta_raw, int dtype, int beta_stride, const void* a_raw,
-                                const float* dt_bias, const float* a_log, float* state, float* o, const int* first_row,
-                                const int* slots, int n_seqs, int heads, int kvheads, int dim, int vdim, int write_state,
-                                int n_slots, cudaStream_t stream) {
-  if (n_seqs <= 0) return 0;
-  if (heads <= 0 || kvheads <= 0 || heads % kvheads || dim <= 0 || dim > PARTS * 64 || vdim <= 0)
-    return fms_fail("delta_rule_scan: %d heads over %d, dim %d (up to %d), vdim %d", heads, kvheads, dim, PARTS * 64, vdim);
-  const dim3 grid(n_seqs, heads, (vdim + VB - 1) / VB), block(VB * PARTS);
-  const size_t smem = ((size_t)3 * CH * dim + CH * VB + CH) * sizeof(float);
+// decay [tokens, heads * dim] and beta [tokens, heads]: float32 scratch of the caller's
+FMS_API int fms_delta_rule_scan(float* qkv, const void* beta_raw, int dtype, int beta_stride, const void* a_raw,
+                                const float* dt_bias, const float* a_log, float* decay, float* beta, float* state, float* o,
+                                const int* first_row, const int* slots, int n_tokens, int n_seqs, int heads, int kvheads,
+                                int dim, int vdim, int write_state, int n_slots, cudaStream_t stream) {
+  if (n_seqs <= 0 || n_tokens <= 0) return 0;
+  if (heads <= 0 || kvheads <= 0 || heads % kvheads || dim <= 0 || dim > PARTS * 32 || vdim <= 0)
+    return fms_fail("delta_rule_scan: %d heads over %d, dim %d (up to %d), vdim %d", heads, kvheads, dim, PARTS * 32, vdim);
+  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(delta_prepare_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, qkv, (const T*)a_raw,
+                                          (const T*)beta_raw, beta_stride, dt_bias, a_log, decay, beta, heads, kvheads, dim,
+                                          vdim));
   const int np = (dim + PARTS - 1) / PARTS;
-#define FMS_SCAN(NP)                                                                                                    \
+  const int vp = columns_per_thread(n_seqs, heads, vdim, np);
+  const long row_w = 2L * kvheads * dim + (long)heads * vdim;
+  const int vec_qk = rows_allow_16(qkv, 0, row_w, dim) && dim % 4 == 0;
+  const int vec_g = rows_allow_16(decay, 0, (long)heads * dim, dim);
+  const int vec_v = rows_allow_16(qkv, 2L * kvheads * dim, row_w, vdim) && vdim % (GROUPS * vp) == 0 && (GROUPS * vp) % 4 == 0;
+  const dim3 grid(n_seqs, heads, (vdim + GROUPS * vp - 1) / (GROUPS * vp)), block(GROUPS * PARTS);
+#define FMS_LAUNCH(NP, VP)                                                                                              \
   do {                                                                                                                  \
-    cudaFuncSetAttribute(delta_rule_scan_kernel<T, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
-    fms_launch(delta_rule_scan_kernel<T, NP>, grid, block, smem, stream, qkv, (const T*)beta_raw, beta_stride,           \
-               (const T*)a_raw, dt_bias, a_log, state, o, first_row, slots, heads, kvheads, dim, vdim, write_state,      \
-               n_slots);                                                                                                 \
+    const size_t smem = ((size_t)2 * CH * (3 * RowLayout<NP>::ROW + GROUPS * VP + 1)) * sizeof(float);                           \
+    cudaFuncSetAttribute(delta_rule_scan_kernel<NP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+    fms_launch(delta_rule_scan_kernel<NP, VP>, grid, block, smem, stream, (const float*)qkv, (const float*)decay,        \
+               (const float*)beta, state, o, first_row, slots, heads, kvheads, dim, vdim, write_state, n_slots, vec_qk,  \
+               vec_g, vec_v);                                                                                            \
   } while (0)
-  FMS_DISPATCH_DTYPE(dtype, T, {
-    if (np <= 8) FMS_SCAN(8);
-    else if (np <= 16) FMS_SCAN(16);
-    else if (np <= 32) FMS_SCAN(32);
-    else FMS_SCAN(64);
-  });
-#undef FMS_SCAN
+  FMS_SCAN_SHAPES(FMS_LAUNCH);
+#undef FMS_LAUNCH
   return fms_launch_status("delta_rule_scan");
 }
 

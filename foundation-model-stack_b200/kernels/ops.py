@@ -76,7 +76,7 @@ _SIGNATURES = {
                                   _P, _P, _P, _P],
     "fms_causal_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "fms_selective_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-    "fms_delta_rule_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "fms_delta_rule_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "fms_gated_group_rmsnorm": [_P, _P, _I, _I, _I, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
@@ -689,17 +689,21 @@ def delta_rule_scan(qkv: torch.Tensor, proj: torch.Tensor, beta_offset: int, a_r
     """Per head, S = diag(g) S; u = beta (v - S^T k); S += k u^T; o = S^T q over each sequence's rows.  ``qkv`` float32
     [tokens, 2 kvheads * dim + heads * vdim] = [q | k | v]; beta = sigmoid(proj[:, beta_offset + head]);
     g = exp(-exp(a_log[head]) softplus(a_raw + dt_bias)), [heads * dim] a row; ``state`` float32 [slots, heads, vdim, dim].
-    Returns o float32 [tokens, heads * vdim]."""
+    q and k of ``qkv`` are made unit vectors in place on the way.  Returns o float32 [tokens, heads * vdim]."""
     n = qkv.shape[0]
     if qkv.dtype != torch.float32 or state.dtype != torch.float32 or qkv.shape[1] != 2 * kvheads * dim + heads * vdim \
             or tuple(state.shape[1:]) != (heads, vdim, dim) or tuple(a_raw.shape) != (n, heads * dim) \
             or a_raw.dtype != proj.dtype:
         raise KernelError("delta_rule_scan: qkv float32 [tokens, q | k | v], state float32 [slots, heads, vdim, dim]")
     o = torch.empty((n, heads * vdim), dtype=torch.float32, device=qkv.device)
+    # decays [tokens, heads * dim], then betas [tokens, heads]
+    scratch = torch.empty((n * heads * (dim + 1),), dtype=torch.float32, device=qkv.device)
     _call("state_scan", "fms_delta_rule_scan", _ptr(qkv), _ptr(proj) + beta_offset * proj.element_size(),
-          _code(proj.dtype), proj.shape[1], _ptr(a_raw), _ptr(dt_bias), _ptr(a_log), _ptr(state), _ptr(o),
-          _ptr(batch.first_row), _ptr(batch.slots), batch.n_seqs, heads, kvheads, dim, vdim, 1 if writes_state else 0,
-          state.shape[0], _stream())
+          _code(proj.dtype), proj.shape[1], _ptr(a_raw), _ptr(dt_bias), _ptr(a_log), scratch.data_ptr(),
+          scratch.data_ptr() + 4 * n * heads * dim, _ptr(state), _ptr(o), _ptr(batch.first_row), _ptr(batch.slots), n,
+          batch.n_seqs, heads, kvheads, dim, vdim, 1 if writes_state else 0, state.shape[0], _stream())
+    global launches
+    launches += 1  # the kernel that makes q, k, the decays and the betas ready
     return o
 
 
