@@ -753,7 +753,7 @@ FMS_API int fms_cast_rows(const float* x, void* out, int dtype, long n, cudaStre
 //   q, k: x / sqrt(mean(x^2) + eps) over the head's dim values, where qk_norm is set (no gain)
 //   q -> q_out[t, head, 0..pad) ; k, v -> the cache row of the token's slot and place, each `pad` wide:
 //   values beyond dim (vdim) are zeros, so that kernels built for one head size `pad` serve both
-// One block per token, a warp per head; float32 arithmetic.
+// A warp per (token, head), four a block; float32 arithmetic.
 // ---------------------------------------------------------------------------------------------------
 constexpr int PREP_MAX_PAIRS = 256;
 
@@ -776,7 +776,8 @@ __global__ void qk_prepare_store_kernel(const T* proj, int stride, T* q_out, con
     sc[i] = make_float2(s, c);
   }
   __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);  // a warp per head
   const T* row = proj + (size_t)t * stride;
   T* krow = nullptr;
   T* vrow = nullptr;
@@ -796,20 +797,20 @@ __global__ void qk_prepare_store_kernel(const T* proj, int stride, T* q_out, con
       }
     }
   }
-  for (int item = warp; item < nheads + 2 * kvheads; item += nwarps) {
+  if (item < nheads + 2 * kvheads) {
     if (item >= nheads + kvheads) {  // a value head: copied and padded
       const int h = item - nheads - kvheads;
-      if (vrow == nullptr) continue;
+      if (vrow == nullptr) return;
       const T* src = row + (size_t)(nheads + kvheads) * dim + (size_t)h * vdim;
       T* dst = vrow + (size_t)h * block_tokens * pad;
       for (int e = lane; e < pad; e += 32) dst[e] = e < vdim ? src[e] : from_f32<T>(0.f);
-      continue;
+      return;
     }
     const bool is_q = item < nheads;
     const T* src = row + (size_t)item * dim;  // q heads, then k heads, all `dim` wide
     T* dst = is_q ? q_out + ((size_t)t * nheads + item) * pad
                   : (krow ? krow + (size_t)(item - nheads) * block_tokens * pad : nullptr);
-    if (dst == nullptr) continue;
+    if (dst == nullptr) return;
     float ss = 0.f;
     for (int i = lane; i < rot / 2; i += 32) {
       const float x0 = to_f32(src[2 * i]), x1 = to_f32(src[2 * i + 1]);
@@ -841,7 +842,8 @@ FMS_API int fms_qk_prepare_store(const void* proj, int dtype, int stride, void* 
     return fms_fail("qk_prepare_store: %d rotated values of %d", rot, dim);
   if (dim <= 0 || vdim <= 0 || pad < dim || pad < vdim) return fms_fail("qk_prepare_store: dim %d, vdim %d, pad %d", dim, vdim, pad);
   FMS_DISPATCH_DTYPE(dtype, T,
-                     fms_launch(qk_prepare_store_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, (const T*)proj, stride,
+                     fms_launch(qk_prepare_store_kernel<T>, dim3(n_tokens, (nheads + 2 * kvheads + 3) / 4), dim3(128), 0, stream,
+                                (const T*)proj, stride,
                                 (T*)q_out, inv_freq, rot, qk_norm, eps, positions, position_ids, token_seq, slots,
                                 (T*)k_cache, (T*)v_cache, table, table_stride, block_tokens, nheads, kvheads, dim, vdim, pad,
                                 write_cache, error_flag, n_seqs, table_rows, pool_blocks));

@@ -31,29 +31,47 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 
 // ---- causal convolution ------------------------------------------------------------------------------
 // x: rows of `stride` values (the convolved channels are its first `channels` from the pointer on); a block per
-// (row, run of 256 channels)
+// (8 rows, run of 256 channels), a thread per channel that walks the rows with its taps in registers
+constexpr int CONV_TOKENS = 8, CONV_CHANNELS = 256;
+
 template <typename T>
 __global__ void causal_conv_kernel(const T* x, int stride, const float* w, const float* bias, const float* tail,
                                    const int* token_seq, const int* first_row, const int* slots, float* out,
                                    int n_tokens, int channels, int taps, int act, int n_seqs, int n_slots) {
+  extern __shared__ float rows[];  // [CONV_TOKENS + taps - 1][CONV_CHANNELS]: the tile's rows and the taps - 1 before them
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
-  if (c >= channels) return;
-  const int seq = token_seq[t];
-  if (!FMS_IN(seq, n_seqs)) return;
-  const int local = t - first_row[seq];  // the row's place among its sequence's rows of this step
-  const int slot = __ldcg(slots + seq);
-  if (!FMS_IN(slot, n_slots)) return;
-  const float* tl = tail + (size_t)slot * (taps - 1) * channels;
-  float acc = bias ? bias[c] : 0.f;
-  for (int j = 0; j < taps; ++j) {
-    const int back = taps - 1 - j;  // how many rows before this one
-    const float v = back <= local ? to_f32(x[(size_t)(t - back) * stride + c])
-                                  : tl[(size_t)(taps - 1 + local - back) * channels + c];
-    acc = fmaf(w[(size_t)c * taps + j], v, acc);
+  const int t0 = blockIdx.x * CONV_TOKENS, c = blockIdx.y * CONV_CHANNELS + threadIdx.x;
+  const bool c_ok = c < channels;
+  for (int r = 0; r < CONV_TOKENS + taps - 1; ++r) {
+    const int t = t0 - (taps - 1) + r;
+    rows[r * CONV_CHANNELS + threadIdx.x] = (c_ok && t >= 0 && t < n_tokens) ? to_f32(x[(size_t)t * stride + c]) : 0.f;
   }
-  out[(size_t)t * channels + c] = act ? acc * sigmoid_f(acc) : acc;
+  // every thread reads only what it wrote itself: no barrier is needed
+  if (!c_ok) return;
+  float wt[MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+  const float b = bias ? bias[c] : 0.f;
+  for (int i = 0; i < CONV_TOKENS && t0 + i < n_tokens; ++i) {
+    const int t = t0 + i;
+    const int seq = token_seq[t];
+    if (!FMS_IN(seq, n_seqs)) continue;
+    const int local = t - first_row[seq];  // the row's place among its sequence's rows of this step
+    const int slot = __ldcg(slots + seq);
+    if (!FMS_IN(slot, n_slots)) continue;
+    const float* tl = tail + (size_t)slot * (taps - 1) * channels;
+    float acc = b;
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j) {
+      if (j >= taps) break;
+      const int back = taps - 1 - j;  // how many rows before this one
+      const float v = back <= local ? rows[(i + j) * CONV_CHANNELS + threadIdx.x]
+                                    : tl[(size_t)(taps - 1 + local - back) * channels + c];
+      acc = fmaf(wt[j], v, acc);
+    }
+    out[(size_t)t * channels + c] = act ? acc * sigmoid_f(acc) : acc;
+  }
 }
 
 // the tail after the step: the last taps - 1 inputs of (old tail, the step's rows); one thread per (sequence, channel)
@@ -155,6 +173,36 @@ __device__ __forceinline__ void stage_runs(float* dst, const float* src, size_t 
   }
 }
 
+// a thread's NP state rows of one value column, from and to global memory: 16 bytes at a time where the state has
+// exactly PARTS * NP rows (the eight threads of a column then cover its row of `rows` values without a gap)
+template <int NP> __device__ __forceinline__ void load_state(const float* st, int part, int rows, bool valid, float (&r)[NP]) {
+  if (NP % 4 == 0 && rows == PARTS * NP) {
+    if (valid) load_run<NP>(st + part * NP, r);
+    else {
+#pragma unroll
+      for (int j = 0; j < NP; ++j) r[j] = 0.f;
+    }
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < NP; ++j) {
+    const int n = part * NP + j;
+    r[j] = (valid && n < rows) ? st[n] : 0.f;
+  }
+}
+template <int NP> __device__ __forceinline__ void store_state(float* st, int part, int rows, const float (&r)[NP]) {
+  if (NP % 4 == 0 && rows == PARTS * NP) {
+#pragma unroll
+    for (int j = 0; j < NP; j += 4) *reinterpret_cast<float4*>(st + part * NP + j) = make_float4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < NP; ++j) {
+    const int n = part * NP + j;
+    if (n < rows) st[n] = r[j];
+  }
+}
+
 __device__ __forceinline__ float octet_sum(float v) {
   v += __shfl_xor_sync(0xffffffffu, v, 1);
   v += __shfl_xor_sync(0xffffffffu, v, 2);
@@ -194,12 +242,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const float* xbc, c
 #pragma unroll
   for (int i = 0; i < VP; ++i) {
     const int v = v0 + grp * VP + i;
-    const float* st = state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * n_state;
-#pragma unroll
-    for (int j = 0; j < NP; ++j) {
-      const int n = part * NP + j;
-      s[i][j] = (v < vdim && n < n_state) ? st[n] : 0.f;
-    }
+    load_state<NP>(state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * n_state, part, n_state, v < vdim, s[i]);
   }
   __syncthreads();
   auto issue = [&](int c0, int stage) {
@@ -264,18 +307,13 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const float* xbc, c
     for (int i = 0; i < VP; ++i) {
       const int v = v0 + grp * VP + i;
       if (v >= vdim) continue;
-      float* st = state + (((size_t)slot * heads + head) * vdim + v) * n_state;
-#pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        const int n = part * NP + j;
-        if (n < n_state) st[n] = s[i][j];
-      }
+      store_state<NP>(state + (((size_t)slot * heads + head) * vdim + v) * n_state, part, n_state, s[i]);
     }
   }
 }
 
 // ---- gated delta rule --------------------------------------------------------------------------------
-// What enters the recurrence, made ready for every token at once (one block per token, a warp per head):
+// What enters the recurrence, made ready for every token at once (a warp per token and head):
 //   qkv [tokens, 2 kvheads * dim + heads * vdim] float32 (after the convolution): q | k | v;  q and k of every key head
 //   become unit vectors in place, x / sqrt(sum(x^2) + 1e-6), q also times dim^-1/2
 //   decay[t, h, n] = exp(-exp(a_log[h]) * softplus(a_raw[t, h, n] + dt_bias[h, n]));  beta[t, h] = sigmoid(beta_raw[t, h])
@@ -285,10 +323,11 @@ __global__ void delta_prepare_kernel(float* qkv, const T* a_raw, const T* beta_r
                                      int vdim) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int t = blockIdx.x, lane = threadIdx.x & 31;
   const int row_w = 2 * kvheads * dim + heads * vdim;
   const float q_scale = 1.f / sqrtf((float)dim);
-  for (int item = warp; item < 2 * kvheads + heads; item += nwarps) {
+  const int item = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);  // a warp per head
+  if (item < 2 * kvheads + heads) {
     if (item < 2 * kvheads) {  // q heads, then k heads
       float* x = qkv + (size_t)t * row_w + (size_t)item * dim;
       float ss = 0.f;
@@ -332,12 +371,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(const float* qkv, 
 #pragma unroll
   for (int i = 0; i < VP; ++i) {
     const int v = v0 + grp * VP + i;
-    const float* st = state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * dim;
-#pragma unroll
-    for (int j = 0; j < NP; ++j) {
-      const int n = part * NP + j;
-      s[i][j] = (v < vdim && n < dim) ? st[n] : 0.f;
-    }
+    load_state<NP>(state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * dim, part, dim, v < vdim, s[i]);
   }
   __syncthreads();
   auto issue = [&](int c0, int stage) {
@@ -410,12 +444,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(const float* qkv, 
     for (int i = 0; i < VP; ++i) {
       const int v = v0 + grp * VP + i;
       if (v >= vdim) continue;
-      float* st = state + (((size_t)slot * heads + head) * vdim + v) * dim;
-#pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        const int n = part * NP + j;
-        if (n < dim) st[n] = s[i][j];
-      }
+      store_state<NP>(state + (((size_t)slot * heads + head) * vdim + v) * dim, part, dim, s[i]);
     }
   }
 }
@@ -424,22 +453,24 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(const float* qkv, 
 // x [tokens, width] float32; groups of `gs` values; weight[c % weight_period]; gate: columns of rows of gate_stride
 // values.  gate_mode 1: x * silu(gate) before the norm;  2: sigmoid(gate) after the norm and the weight;  0: none.
 // One warp per (token, group).
-template <typename T>
+// TPU threads per (token, group): a warp, or a block of 256 where the groups are long
+template <typename T, int TPU>
 __global__ void gated_group_rmsnorm_kernel(const float* x, const T* gate, int gate_stride, int gate_mode,
                                            const float* weight, int weight_period, float eps, float factor, T* out,
                                            int n_tokens, int width, int gs) {
+  __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const size_t unit = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x % TPU;
+  const size_t unit = (size_t)blockIdx.x * (blockDim.x / TPU) + (threadIdx.x / TPU);
   const int per_row = width / gs;
-  if (unit >= (size_t)n_tokens * per_row) return;
+  if (unit >= (size_t)n_tokens * per_row) return;  // TPU > 32: one unit a block, so the whole block alike
   const size_t t = unit / per_row;
   const int c0 = (int)(unit - t * per_row) * gs;
   const float* xr = x + t * width + c0;
   const T* gr = gate ? gate + t * gate_stride + c0 : nullptr;
   float ss = 0.f;
-  for (int e = lane; e < gs; e += 32) {
+  for (int e = lane; e < gs; e += TPU) {
     float v = xr[e];
     if (gate_mode == 1) {
       const float z = to_f32(gr[e]);
@@ -447,8 +478,11 @@ __global__ void gated_group_rmsnorm_kernel(const float* x, const T* gate, int ga
     }
     ss = fmaf(v, v, ss);
   }
-  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)gs + eps);
-  for (int e = lane; e < gs; e += 32) {
+  float total;
+  if constexpr (TPU == 32) total = warp_sum(ss);
+  else total = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(total / (float)gs + eps);
+  for (int e = lane; e < gs; e += TPU) {
     float v = xr[e];
     if (gate_mode == 1) {
       const float z = to_f32(gr[e]);
@@ -470,7 +504,8 @@ FMS_API int fms_causal_conv(const void* x, int dtype, int stride, const float* w
   if (n_tokens <= 0) return 0;
   if (taps < 1 || taps > MAX_TAPS) return fms_fail("causal_conv: %d taps (1..%d)", taps, MAX_TAPS);
   FMS_DISPATCH_DTYPE(dtype, T, {
-    fms_launch(causal_conv_kernel<T>, dim3(n_tokens, (channels + 255) / 256), dim3(256), 0, stream, (const T*)x, stride, w,
+    fms_launch(causal_conv_kernel<T>, dim3((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (channels + CONV_CHANNELS - 1) / CONV_CHANNELS),
+               dim3(CONV_CHANNELS), (size_t)(CONV_TOKENS + taps - 1) * CONV_CHANNELS * sizeof(float), stream, (const T*)x, stride, w,
                bias, (const float*)tail, token_seq, first_row, slots, out, n_tokens, channels, taps, act, n_seqs, n_slots);
     if (write_state && taps > 1)
       fms_launch(conv_tail_kernel<T>, dim3((channels + 127) / 128, n_seqs), dim3(128), 0, stream, (const T*)x, stride, tail,
@@ -535,7 +570,7 @@ FMS_API int fms_delta_rule_scan(float* qkv, const void* beta_raw, int dtype, int
   if (n_seqs <= 0 || n_tokens <= 0) return 0;
   if (heads <= 0 || kvheads <= 0 || heads % kvheads || dim <= 0 || dim > PARTS * 32 || vdim <= 0)
     return fms_fail("delta_rule_scan: %d heads over %d, dim %d (up to %d), vdim %d", heads, kvheads, dim, PARTS * 32, vdim);
-  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(delta_prepare_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, qkv, (const T*)a_raw,
+  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(delta_prepare_kernel<T>, dim3(n_tokens, (2 * kvheads + heads + 3) / 4), dim3(128), 0, stream, qkv, (const T*)a_raw,
                                           (const T*)beta_raw, beta_stride, dt_bias, a_log, decay, beta, heads, kvheads, dim,
                                           vdim));
   const int np = (dim + PARTS - 1) / PARTS;
@@ -566,8 +601,14 @@ FMS_API int fms_gated_group_rmsnorm(const float* x, const void* gate, int dtype,
     return fms_fail("gated_group_rmsnorm: rows of %d in groups of %d", width, group_size);
   if (gate_mode != 0 && gate == nullptr) return fms_fail("gated_group_rmsnorm: a gate mode without a gate");
   const size_t units = (size_t)n_tokens * (width / group_size);
-  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(gated_group_rmsnorm_kernel<T>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, stream,
-                                          x, (const T*)gate, gate_stride, gate_mode, weight, weight_period, eps, factor,
-                                          (T*)out, n_tokens, width, group_size));
+  if (group_size >= 512) {
+    FMS_DISPATCH_DTYPE(dtype, T, fms_launch(gated_group_rmsnorm_kernel<T, 256>, dim3((unsigned)units), dim3(256), 0, stream, x,
+                                            (const T*)gate, gate_stride, gate_mode, weight, weight_period, eps, factor,
+                                            (T*)out, n_tokens, width, group_size));
+  } else {
+    FMS_DISPATCH_DTYPE(dtype, T, fms_launch(gated_group_rmsnorm_kernel<T, 32>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0,
+                                            stream, x, (const T*)gate, gate_stride, gate_mode, weight, weight_period, eps,
+                                            factor, (T*)out, n_tokens, width, group_size));
+  }
   return fms_launch_status("gated_group_rmsnorm");
 }
