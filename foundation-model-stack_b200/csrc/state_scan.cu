@@ -31,46 +31,99 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 
 // ---- causal convolution ------------------------------------------------------------------------------
 // x: rows of `stride` values (the convolved channels are its first `channels` from the pointer on); a block per
-// (8 rows, run of 256 channels), a thread per channel that walks the rows with its taps in registers
-constexpr int CONV_TOKENS = 8, CONV_CHANNELS = 256;
+// (8 rows, run of channels), a thread per 4 channels (one where sizes or addresses do not allow 16-byte accesses)
+// with the rows and its taps in registers
+constexpr int CONV_TOKENS = 8, CONV_THREADS = 128;
 
-template <typename T>
-__global__ void causal_conv_kernel(const T* x, int stride, const float* w, const float* bias, const float* tail,
-                                   const int* token_seq, const int* first_row, const int* slots, float* out,
-                                   int n_tokens, int channels, int taps, int act, int n_seqs, int n_slots) {
-  extern __shared__ float rows[];  // [CONV_TOKENS + taps - 1][CONV_CHANNELS]: the tile's rows and the taps - 1 before them
+template <int CPT> __device__ __forceinline__ void load_channels(const float* p, float (&v)[CPT]) {
+  if constexpr (CPT == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) v[k] = p[k];
+  }
+}
+template <int CPT> __device__ __forceinline__ void load_channels(const __nv_bfloat16* p, float (&v)[CPT]) {
+  if constexpr (CPT == 4) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+  } else {
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) v[k] = __bfloat162float(p[k]);
+  }
+}
+
+// A thread takes CPT consecutive channels of CONV_TOKENS consecutive rows; TMAX bounds the taps (4 or MAX_TAPS).
+template <typename T, int CPT, int TMAX>
+__global__ void __launch_bounds__(CONV_THREADS) causal_conv_kernel(const T* x, int stride, const float* w, const float* bias,
+                                                                   const float* tail, const int* token_seq,
+                                                                   const int* first_row, const int* slots, float* out,
+                                                                   int n_tokens, int channels, int taps, int act,
+                                                                   int n_seqs, int n_slots) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t0 = blockIdx.x * CONV_TOKENS, c = blockIdx.y * CONV_CHANNELS + threadIdx.x;
-  const bool c_ok = c < channels;
-  for (int r = 0; r < CONV_TOKENS + taps - 1; ++r) {
+  const int t0 = blockIdx.x * CONV_TOKENS, c = (blockIdx.y * CONV_THREADS + threadIdx.x) * CPT;
+  if (c >= channels) return;
+  // everything the thread reads is asked for at once: the tile's rows and the taps - 1 before them, the taps, and
+  // where each of the tile's tokens belongs
+  float xs[CONV_TOKENS + TMAX - 1][CPT];  // xs[r]: row t0 - (taps - 1) + r
+#pragma unroll
+  for (int r = 0; r < CONV_TOKENS + TMAX - 1; ++r) {
     const int t = t0 - (taps - 1) + r;
-    rows[r * CONV_CHANNELS + threadIdx.x] = (c_ok && t >= 0 && t < n_tokens) ? to_f32(x[(size_t)t * stride + c]) : 0.f;
-  }
-  // every thread reads only what it wrote itself: no barrier is needed
-  if (!c_ok) return;
-  float wt[MAX_TAPS];
+    if (r < CONV_TOKENS + taps - 1 && t >= 0 && t < n_tokens) load_channels<CPT>(x + (size_t)t * stride + c, xs[r]);
+    else {
 #pragma unroll
-  for (int j = 0; j < MAX_TAPS; ++j) wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
-  const float b = bias ? bias[c] : 0.f;
-  for (int i = 0; i < CONV_TOKENS && t0 + i < n_tokens; ++i) {
-    const int t = t0 + i;
-    const int seq = token_seq[t];
-    if (!FMS_IN(seq, n_seqs)) continue;
-    const int local = t - first_row[seq];  // the row's place among its sequence's rows of this step
-    const int slot = __ldcg(slots + seq);
-    if (!FMS_IN(slot, n_slots)) continue;
-    const float* tl = tail + (size_t)slot * (taps - 1) * channels;
-    float acc = b;
-#pragma unroll
-    for (int j = 0; j < MAX_TAPS; ++j) {
-      if (j >= taps) break;
-      const int back = taps - 1 - j;  // how many rows before this one
-      const float v = back <= local ? rows[(i + j) * CONV_CHANNELS + threadIdx.x]
-                                    : tl[(size_t)(taps - 1 + local - back) * channels + c];
-      acc = fmaf(wt[j], v, acc);
+      for (int k = 0; k < CPT; ++k) xs[r][k] = 0.f;
     }
-    out[(size_t)t * channels + c] = act ? acc * sigmoid_f(acc) : acc;
+  }
+  float wt[CPT][TMAX], b[CPT];
+#pragma unroll
+  for (int k = 0; k < CPT; ++k) {
+#pragma unroll
+    for (int j = 0; j < TMAX; ++j) wt[k][j] = j < taps ? w[(size_t)(c + k) * taps + j] : 0.f;
+    b[k] = bias ? bias[c + k] : 0.f;
+  }
+  int local[CONV_TOKENS], slot[CONV_TOKENS];
+#pragma unroll
+  for (int i = 0; i < CONV_TOKENS; ++i) {
+    local[i] = -1;
+    slot[i] = 0;
+    if (t0 + i < n_tokens) {
+      const int seq = token_seq[t0 + i];
+      if (FMS_IN(seq, n_seqs)) {
+        local[i] = t0 + i - first_row[seq];  // the row's place among its sequence's rows of this step
+        slot[i] = __ldcg(slots + seq);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CONV_TOKENS; ++i) {
+    if (local[i] < 0 || !FMS_IN(slot[i], n_slots)) continue;
+    const float* tl = tail + (size_t)slot[i] * (taps - 1) * channels;
+    float acc[CPT];
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) acc[k] = b[k];
+#pragma unroll
+    for (int j = 0; j < TMAX; ++j) {
+      if (j < taps) {
+        const int back = taps - 1 - j;  // how many rows before this one
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) {
+          const float v = back <= local[i] ? xs[i + j][k] : tl[(size_t)(taps - 1 + local[i] - back) * channels + c + k];
+          acc[k] = fmaf(wt[k][j], v, acc[k]);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) acc[k] = act ? acc[k] * sigmoid_f(acc[k]) : acc[k];
+    float* o = out + (size_t)(t0 + i) * channels + c;
+    if constexpr (CPT == 4) *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    else {
+#pragma unroll
+      for (int k = 0; k < CPT; ++k) o[k] = acc[k];
+    }
   }
 }
 
@@ -503,14 +556,23 @@ FMS_API int fms_causal_conv(const void* x, int dtype, int stride, const float* w
                             cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (taps < 1 || taps > MAX_TAPS) return fms_fail("causal_conv: %d taps (1..%d)", taps, MAX_TAPS);
+  const size_t item = dtype == FMS_BF16 ? 2 : 4;
+  const bool four = channels % 4 == 0 && stride % 4 == 0 && (uintptr_t)x % (4 * item) == 0 && (uintptr_t)out % 16 == 0;
+  const int cpt = four ? 4 : 1;
+  const dim3 grid((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (channels / cpt + CONV_THREADS - 1) / CONV_THREADS);
+#define FMS_CONV(CPT, TMAX)                                                                                          \
+  fms_launch(causal_conv_kernel<T, CPT, TMAX>, grid, dim3(CONV_THREADS), 0, stream, (const T*)x, stride, w, bias,     \
+             (const float*)tail, token_seq, first_row, slots, out, n_tokens, channels, taps, act, n_seqs, n_slots)
   FMS_DISPATCH_DTYPE(dtype, T, {
-    fms_launch(causal_conv_kernel<T>, dim3((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (channels + CONV_CHANNELS - 1) / CONV_CHANNELS),
-               dim3(CONV_CHANNELS), (size_t)(CONV_TOKENS + taps - 1) * CONV_CHANNELS * sizeof(float), stream, (const T*)x, stride, w,
-               bias, (const float*)tail, token_seq, first_row, slots, out, n_tokens, channels, taps, act, n_seqs, n_slots);
+    if (four && taps <= 4) FMS_CONV(4, 4);
+    else if (four) FMS_CONV(4, MAX_TAPS);
+    else if (taps <= 4) FMS_CONV(1, 4);
+    else FMS_CONV(1, MAX_TAPS);
     if (write_state && taps > 1)
       fms_launch(conv_tail_kernel<T>, dim3((channels + 127) / 128, n_seqs), dim3(128), 0, stream, (const T*)x, stride, tail,
                  first_row, slots, channels, taps, n_seqs, n_slots);
   });
+#undef FMS_CONV
   return fms_launch_status("causal_conv");
 }
 

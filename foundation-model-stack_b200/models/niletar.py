@@ -59,9 +59,14 @@ class NiletarConfig(ModelConfig):
             if mlp is not None and mlp.get("kind") != "dense":
                 raise ValueError(f"layer {i}: feed-forward kind {mlp.get('kind')!r}; known: dense, or null for none")
             j = layer.get("weights_of")
-            if j is not None and not (0 <= int(j) < i and self.layers[int(j)].get("weights_of") is None
-                                      and self.layers[int(j)]["type"] == layer["type"]):
-                raise ValueError(f"layer {i}: weights_of {j} names no earlier layer of its type with weights of its own")
+            if j is not None and not (0 <= int(j) < i and self.layers[int(j)]["type"] == layer["type"]):
+                raise ValueError(f"layer {i}: weights_of {j} names no earlier layer of its type")
+
+    def owner_of(self, i: int) -> int:
+        """The layer whose tensors layer i runs with: itself, or where its chain of ``weights_of`` ends."""
+        while self.layers[i].get("weights_of") is not None:
+            i = int(self.layers[i]["weights_of"])
+        return i
 
 
 def _config_from_json(values: Dict[str, Any]) -> NiletarConfig:
@@ -159,7 +164,8 @@ class Niletar(Model):
                                                 ("high_freq_factor", float(scaling["high"])),
                                                 ("original_max_position_embeddings", float(scaling["original"]))))
         left_spec = MixerSpec("sink_attention", dim=c.width, nheads=int(left["heads"]), kvheads=int(left["kv_heads"]),
-                              head_dim=int(left["dim"]), bias=True, scale=float(left["scale"]), position=position,
+                              head_dim=int(left["dim"]), bias=True,
+                              scale=float(left["scale"]) if left.get("scale") is not None else None, position=position,
                               options=(("vdim", int(left["vdim"])), ("rot_dims", int(rot.get("dims", 0))), ("qk_norm", True),
                                        ("eps", eps), ("sink", True), ("gate", True)))
         right_spec = MixerSpec("gated_delta_rule", dim=c.width, nheads=int(right["heads"]), kvheads=int(right["kv_heads"]),
@@ -179,7 +185,7 @@ class Niletar(Model):
             ff = None
             if layer.get("mlp") is not None:
                 ff = FeedForwardSpec("glu", dim=c.width, hidden=int(layer["mlp"]["ff"]), activation="silu")
-            j = layer.get("weights_of")
+            j = None if layer.get("weights_of") is None else c.owner_of(len(blocks))
             blocks.append(BlockSpec(mixer=self._mixer_spec(layer), feed_forward=ff, mixer_norm=norm,
                                     feed_forward_norm=norm if ff is not None else None, arrangement="post_norm",
                                     names=("norm1", "mix", "norm2", "mlp"), options=(("alpha", float(c.postln_alpha)),),

@@ -92,6 +92,10 @@ def test_config_json_of_another_design_or_with_unknown_layers_is_refused():
     bad["layers"][0]["type"] = "convolution"
     with pytest.raises(ValueError, match="convolution"):
         Niletar.config_from_json(bad)
+    chained = json.loads(json.dumps(nm.CONFIGS["p"]))
+    chained["layers"].append(dict(chained["layers"][2], weights_of=2))  # the weights of a layer that takes another's
+    spec = Niletar(Niletar.config_from_json(chained)).decoder_spec()
+    assert [b.weights_of for b in spec.layers] == [None, None, 1, 0, 1]
     bad = json.loads(json.dumps(nm.CONFIGS["p"]))
     bad["layers"][2]["weights_of"] = 0  # a layer of another type
     with pytest.raises(ValueError, match="weights_of"):
