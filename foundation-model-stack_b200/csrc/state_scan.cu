@@ -23,7 +23,6 @@
 // is declared __restrict__, and what the kernel right before wrote is read after griddepcontrol.wait.
 namespace {
 constexpr int CH = 16;      // tokens brought into shared memory at a time
-constexpr int PARTS = 8;    // threads that share a group of value columns
 constexpr int MAX_TAPS = 16;
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
@@ -156,11 +155,11 @@ __global__ void conv_tail_kernel(const T* x, int stride, float* tail, const int*
 // ---- the two scans ------------------------------------------------------------------------------------
 // Both walk a sequence's tokens in order with the state in registers.  A block of 128 threads owns (sequence, head,
 // run of VB = 16 * VP value columns); a thread owns VP columns and NP consecutive state rows of each, and the eight
-// threads (PARTS) that share a column group add their sums by shuffles, so a column's sum runs over its rows in the
+// (or 16, or 32: PARTS) threads that share a column group add their sums by shuffles, so a column's sum runs over its rows in the
 // same order whatever VP is, whatever else is in the batch and however the prompt was cut.  The tokens' vectors
 // come through shared memory CH tokens at a time by cp.async into two stages: the next chunk is on its way while this
 // one is walked.  Rows of shared memory are padded to PARTS * NP values with zeros, so the inner loops need no bounds.
-constexpr int GROUPS = 16;  // column groups of a block (GROUPS * PARTS = 128 threads)
+constexpr int SCAN_THREADS = 128;  // PARTS threads share a group of value columns; a block has 128 / PARTS groups
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -191,7 +190,7 @@ __device__ __forceinline__ void stage_rows(float* dst, int dst_stride, const flo
 
 // A row of shared memory holds PARTS runs of NP values, one per thread of a column group.  From NP = 8 on the runs lie
 // NP + 4 values apart, so that the eight 16-byte loads of a group's threads fall into different banks.
-template <int NP> struct RowLayout {
+template <int NP, int PARTS> struct RowLayout {
   static constexpr int RUN = NP >= 8 ? NP + 4 : NP;
   static constexpr int ROW = PARTS * RUN;
   __device__ static __forceinline__ int at(int n) { return (n / NP) * RUN + (n % NP); }
@@ -209,9 +208,9 @@ template <int NP> __device__ __forceinline__ void load_run(const float* p, float
   }
 }
 // `count` floats of each of `rows` global rows into shared rows of the padded layout
-template <int NP>
+template <int NP, int PARTS>
 __device__ __forceinline__ void stage_runs(float* dst, const float* src, size_t src_stride, int rows, int count, bool vec) {
-  using L = RowLayout<NP>;
+  using L = RowLayout<NP, PARTS>;
   if (vec) {
     const int per = count >> 2;
     for (int i = threadIdx.x; i < rows * per; i += blockDim.x) {
@@ -227,8 +226,8 @@ __device__ __forceinline__ void stage_runs(float* dst, const float* src, size_t 
 }
 
 // a thread's NP state rows of one value column, from and to global memory: 16 bytes at a time where the state has
-// exactly PARTS * NP rows (the eight threads of a column then cover its row of `rows` values without a gap)
-template <int NP> __device__ __forceinline__ void load_state(const float* st, int part, int rows, bool valid, float (&r)[NP]) {
+// exactly PARTS * NP rows (the threads of a column group then cover a column's `rows` values without a gap)
+template <int NP, int PARTS> __device__ __forceinline__ void load_state(const float* st, int part, int rows, bool valid, float (&r)[NP]) {
   if (NP % 4 == 0 && rows == PARTS * NP) {
     if (valid) load_run<NP>(st + part * NP, r);
     else {
@@ -243,7 +242,7 @@ template <int NP> __device__ __forceinline__ void load_state(const float* st, in
     r[j] = (valid && n < rows) ? st[n] : 0.f;
   }
 }
-template <int NP> __device__ __forceinline__ void store_state(float* st, int part, int rows, const float (&r)[NP]) {
+template <int NP, int PARTS> __device__ __forceinline__ void store_state(float* st, int part, int rows, const float (&r)[NP]) {
   if (NP % 4 == 0 && rows == PARTS * NP) {
 #pragma unroll
     for (int j = 0; j < NP; j += 4) *reinterpret_cast<float4*>(st + part * NP + j) = make_float4(r[j], r[j + 1], r[j + 2], r[j + 3]);
@@ -256,24 +255,23 @@ template <int NP> __device__ __forceinline__ void store_state(float* st, int par
   }
 }
 
-__device__ __forceinline__ float octet_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 1);
-  v += __shfl_xor_sync(0xffffffffu, v, 2);
-  v += __shfl_xor_sync(0xffffffffu, v, 4);
+template <int PARTS> __device__ __forceinline__ float group_sum(float v) {  // over PARTS neighbouring lanes
+#pragma unroll
+  for (int o = 1; o < PARTS; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
 
 // ---- selective state-space scan ----------------------------------------------------------------------
 // xbc [tokens, inner + 2 groups * N] float32 (after the convolution): x | B | C;  dt_raw: column `head` of rows of
 // `dt_stride` values (bfloat16 or float32);  y [tokens, inner] float32.
-template <int NP, int VP>
-__global__ void __launch_bounds__(128) selective_scan_kernel(const float* xbc, const void* dt_raw, int dt_is_bf16,
+template <int NP, int VP, int PARTS>
+__global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const float* xbc, const void* dt_raw, int dt_is_bf16,
                                                              int dt_stride, const float* dt_bias, const float* a_log,
                                                              const float* d_skip, float* state, float* y,
                                                              const int* first_row, const int* slots, int heads, int vdim,
                                                              int n_state, int groups, int write_state, int n_slots,
                                                              int vec_bc, int vec_x) {
-  constexpr int NPAD = RowLayout<NP>::ROW, RUN = RowLayout<NP>::RUN, VB = GROUPS * VP;
+  constexpr int GROUPS = SCAN_THREADS / PARTS, NPAD = RowLayout<NP, PARTS>::ROW, RUN = RowLayout<NP, PARTS>::RUN, VB = GROUPS * VP;
   extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -295,15 +293,15 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const float* xbc, c
 #pragma unroll
   for (int i = 0; i < VP; ++i) {
     const int v = v0 + grp * VP + i;
-    load_state<NP>(state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * n_state, part, n_state, v < vdim, s[i]);
+    load_state<NP, PARTS>(state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * n_state, part, n_state, v < vdim, s[i]);
   }
   __syncthreads();
   auto issue = [&](int c0, int stage) {
     const int cn = min(CH, hi - c0);
     float* base = smem + stage * STAGE;
     const float* src = xbc + (size_t)c0 * row_w;
-    stage_runs<NP>(base, src + inner + (size_t)group * n_state, row_w, cn, n_state, vec_bc);
-    stage_runs<NP>(base + CH * NPAD, src + inner + (size_t)(groups + group) * n_state, row_w, cn, n_state, vec_bc);
+    stage_runs<NP, PARTS>(base, src + inner + (size_t)group * n_state, row_w, cn, n_state, vec_bc);
+    stage_runs<NP, PARTS>(base + CH * NPAD, src + inner + (size_t)(groups + group) * n_state, row_w, cn, n_state, vec_bc);
     stage_rows(base + 2 * CH * NPAD, VB, src + (size_t)head * vdim + v0, row_w, cn, cols, vec_x);
     cp_async_commit();
   };
@@ -348,7 +346,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const float* xbc, c
       }
 #pragma unroll
       for (int i = 0; i < VP; ++i) {
-        acc[i] = octet_sum(acc[i]);
+        acc[i] = group_sum<PARTS>(acc[i]);
         const int v = v0 + grp * VP + i;
         if (part == i && v < vdim) y[(size_t)(c0 + t) * inner + (size_t)head * vdim + v] = fmaf(D, xv[i], acc[i]);
       }
@@ -360,7 +358,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const float* xbc, c
     for (int i = 0; i < VP; ++i) {
       const int v = v0 + grp * VP + i;
       if (v >= vdim) continue;
-      store_state<NP>(state + (((size_t)slot * heads + head) * vdim + v) * n_state, part, n_state, s[i]);
+      store_state<NP, PARTS>(state + (((size_t)slot * heads + head) * vdim + v) * n_state, part, n_state, s[i]);
     }
   }
 }
@@ -399,13 +397,13 @@ __global__ void delta_prepare_kernel(float* qkv, const T* a_raw, const T* beta_r
 }
 
 // qkv as delta_prepare_kernel left it; decay [tokens, heads * dim], beta [tokens, heads]; o [tokens, heads * vdim]
-template <int NP, int VP>
-__global__ void __launch_bounds__(128) delta_rule_scan_kernel(const float* qkv, const float* decay, const float* beta,
+template <int NP, int VP, int PARTS>
+__global__ void __launch_bounds__(SCAN_THREADS) delta_rule_scan_kernel(const float* qkv, const float* decay, const float* beta,
                                                               float* state, float* o, const int* first_row,
                                                               const int* slots, int heads, int kvheads, int dim, int vdim,
                                                               int write_state, int n_slots, int vec_qk, int vec_g,
                                                               int vec_v) {
-  constexpr int NPAD = RowLayout<NP>::ROW, RUN = RowLayout<NP>::RUN, VB = GROUPS * VP;
+  constexpr int GROUPS = SCAN_THREADS / PARTS, NPAD = RowLayout<NP, PARTS>::ROW, RUN = RowLayout<NP, PARTS>::RUN, VB = GROUPS * VP;
   extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -424,16 +422,16 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(const float* qkv, 
 #pragma unroll
   for (int i = 0; i < VP; ++i) {
     const int v = v0 + grp * VP + i;
-    load_state<NP>(state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * dim, part, dim, v < vdim, s[i]);
+    load_state<NP, PARTS>(state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * dim, part, dim, v < vdim, s[i]);
   }
   __syncthreads();
   auto issue = [&](int c0, int stage) {
     const int cn = min(CH, hi - c0);
     float* base = smem + stage * STAGE;
     const float* src = qkv + (size_t)c0 * row_w;
-    stage_runs<NP>(base, src + (size_t)kvh * dim, row_w, cn, dim, vec_qk);
-    stage_runs<NP>(base + CH * NPAD, src + (size_t)(kvheads + kvh) * dim, row_w, cn, dim, vec_qk);
-    stage_runs<NP>(base + 2 * CH * NPAD, decay + ((size_t)c0 * heads + head) * dim, (size_t)heads * dim, cn, dim, vec_g);
+    stage_runs<NP, PARTS>(base, src + (size_t)kvh * dim, row_w, cn, dim, vec_qk);
+    stage_runs<NP, PARTS>(base + CH * NPAD, src + (size_t)(kvheads + kvh) * dim, row_w, cn, dim, vec_qk);
+    stage_runs<NP, PARTS>(base + 2 * CH * NPAD, decay + ((size_t)c0 * heads + head) * dim, (size_t)heads * dim, cn, dim, vec_g);
     stage_rows(base + 3 * CH * NPAD, VB, src + 2 * (size_t)kvheads * dim + (size_t)head * vdim + v0, row_w, cn, cols, vec_v);
     stage_rows(base + 3 * CH * NPAD + CH * VB, 1, beta + (size_t)c0 * heads + head, heads, cn, 1, false);
     cp_async_commit();
@@ -471,7 +469,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(const float* qkv, 
       const float bt = sbeta[t];
 #pragma unroll
       for (int i = 0; i < VP; ++i) {
-        u[i] = bt * (sv[t * VB + grp * VP + i] - octet_sum(acc[i]));
+        u[i] = bt * (sv[t * VB + grp * VP + i] - group_sum<PARTS>(acc[i]));
         acc[i] = 0.f;
       }
 #pragma unroll
@@ -485,7 +483,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(const float* qkv, 
       }
 #pragma unroll
       for (int i = 0; i < VP; ++i) {
-        acc[i] = octet_sum(acc[i]);
+        acc[i] = group_sum<PARTS>(acc[i]);
         const int v = v0 + grp * VP + i;
         if (part == i && v < vdim) o[(size_t)(c0 + t) * heads * vdim + (size_t)head * vdim + v] = acc[i];
       }
@@ -497,7 +495,7 @@ __global__ void __launch_bounds__(128) delta_rule_scan_kernel(const float* qkv, 
     for (int i = 0; i < VP; ++i) {
       const int v = v0 + grp * VP + i;
       if (v >= vdim) continue;
-      store_state<NP>(state + (((size_t)slot * heads + head) * vdim + v) * dim, part, dim, s[i]);
+      store_state<NP, PARTS>(state + (((size_t)slot * heads + head) * vdim + v) * dim, part, dim, s[i]);
     }
   }
 }
@@ -576,25 +574,57 @@ FMS_API int fms_causal_conv(const void* x, int dtype, int stride, const float* w
   return fms_launch_status("causal_conv");
 }
 
-// how many value columns a thread takes: as many as leave every multiprocessor four blocks, whose warps hide one
-// another's latencies (the sums do not depend on it)
-static int columns_per_thread(int n_seqs, int heads, int vdim, int np) {
-  const int most = np >= 32 ? 2 : 4;
-  for (int vp = most; vp > 1; vp >>= 1)
-    if ((long)n_seqs * heads * ((vdim + GROUPS * vp - 1) / (GROUPS * vp)) >= 592 && vdim >= GROUPS * vp) return vp;
-  return 1;
+// How a scan is cut.  PARTS threads share a group of value columns and each holds NP of the state's rows: 8 threads
+// by default; 16 or 32 where a model has so few heads and value columns that a single sequence would leave most
+// multiprocessors idle (the choice looks at the model's sizes only, never at the batch, so a sequence's sums run in the
+// same order whatever it is batched with).  VP value columns a thread: as many as still leave every multiprocessor
+// four blocks, whose warps hide one another's latencies (the sums do not depend on it).
+struct ScanShape {
+  int parts, np, vp;
+};
+static ScanShape scan_shape(int n_seqs, int heads, int vdim, int rows) {
+  ScanShape s;
+  s.parts = 8;
+  if ((long)heads * ((vdim + 15) / 16) < 148 && rows >= 64) s.parts = 16;
+  if (s.parts == 16 && (long)heads * ((vdim + 7) / 8) < 148 && rows >= 128) s.parts = 32;
+  const int need = (rows + s.parts - 1) / s.parts;
+  s.np = need <= 2 ? 2 : (need <= 4 ? 4 : (need <= 8 ? 8 : (need <= 16 ? 16 : 32)));
+  const int groups = SCAN_THREADS / s.parts;
+  s.vp = 1;
+  for (int vp = s.np >= 32 ? 2 : 4; vp > 1; vp >>= 1)
+    if ((long)n_seqs * heads * ((vdim + groups * vp - 1) / (groups * vp)) >= 592 && vdim >= groups * vp) {
+      s.vp = vp;
+      break;
+    }
+  return s;
 }
 static bool rows_allow_16(const void* base, long offset, long stride, int count) {
   return ((uintptr_t)base % 16 == 0) && offset % 4 == 0 && stride % 4 == 0 && count % 4 == 0;
 }
 
-#define FMS_SCAN_SHAPES(LAUNCH)                                   \
-  do {                                                            \
-    if (np <= 2) { if (vp == 4) LAUNCH(2, 4); else if (vp == 2) LAUNCH(2, 2); else LAUNCH(2, 1); }            \
-    else if (np <= 4) { if (vp == 4) LAUNCH(4, 4); else if (vp == 2) LAUNCH(4, 2); else LAUNCH(4, 1); }       \
-    else if (np <= 8) { if (vp == 4) LAUNCH(8, 4); else if (vp == 2) LAUNCH(8, 2); else LAUNCH(8, 1); }       \
-    else if (np <= 16) { if (vp == 4) LAUNCH(16, 4); else if (vp == 2) LAUNCH(16, 2); else LAUNCH(16, 1); }   \
-    else { if (vp == 2) LAUNCH(32, 2); else LAUNCH(32, 1); }                                                  \
+#define FMS_SCAN_VP(LAUNCH, NP, PARTS)                                                  \
+  do {                                                                                  \
+    if (shape.vp == 4) LAUNCH(NP, 4, PARTS);                                             \
+    else if (shape.vp == 2) LAUNCH(NP, 2, PARTS);                                        \
+    else LAUNCH(NP, 1, PARTS);                                                           \
+  } while (0)
+#define FMS_SCAN_VP2(LAUNCH, NP, PARTS)                                                 \
+  do {                                                                                  \
+    if (shape.vp >= 2) LAUNCH(NP, 2, PARTS);                                             \
+    else LAUNCH(NP, 1, PARTS);                                                           \
+  } while (0)
+#define FMS_SCAN_SHAPES(LAUNCH)                                                                        \
+  do {                                                                                                 \
+    if (shape.parts == 8) {                                                                            \
+      if (shape.np == 2) FMS_SCAN_VP(LAUNCH, 2, 8); else if (shape.np == 4) FMS_SCAN_VP(LAUNCH, 4, 8);  \
+      else if (shape.np == 8) FMS_SCAN_VP(LAUNCH, 8, 8); else if (shape.np == 16) FMS_SCAN_VP(LAUNCH, 16, 8); \
+      else FMS_SCAN_VP2(LAUNCH, 32, 8);                                                                \
+    } else if (shape.parts == 16) {                                                                    \
+      if (shape.np <= 4) FMS_SCAN_VP(LAUNCH, 4, 16); else if (shape.np == 8) FMS_SCAN_VP(LAUNCH, 8, 16); \
+      else FMS_SCAN_VP(LAUNCH, 16, 16);                                                                \
+    } else {                                                                                           \
+      if (shape.np <= 4) FMS_SCAN_VP(LAUNCH, 4, 32); else FMS_SCAN_VP(LAUNCH, 8, 32);                   \
+    }                                                                                                  \
   } while (0)
 
 FMS_API int fms_selective_scan(const float* xbc, const void* dt_raw, int dtype, int dt_stride, const float* dt_bias,
@@ -602,20 +632,20 @@ FMS_API int fms_selective_scan(const float* xbc, const void* dt_raw, int dtype, 
                                const int* slots, int n_seqs, int heads, int vdim, int n_state, int groups,
                                int write_state, int n_slots, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
-  if (heads <= 0 || groups <= 0 || heads % groups || n_state <= 0 || n_state > PARTS * 32 || vdim <= 0)
-    return fms_fail("selective_scan: %d heads, %d groups, state %d (up to %d), vdim %d", heads, groups, n_state, PARTS * 32, vdim);
+  if (heads <= 0 || groups <= 0 || heads % groups || n_state <= 0 || n_state > 256 || vdim <= 0)
+    return fms_fail("selective_scan: %d heads, %d groups, state %d (up to 256), vdim %d", heads, groups, n_state, vdim);
   if (dtype != FMS_F32 && dtype != FMS_BF16) return fms_fail("selective_scan: dtype code %d", dtype);
-  const int np = (n_state + PARTS - 1) / PARTS;
-  const int vp = columns_per_thread(n_seqs, heads, vdim, np);
+  const ScanShape shape = scan_shape(n_seqs, heads, vdim, n_state);
+  const int vb = SCAN_THREADS / shape.parts * shape.vp;  // value columns of a block
   const long row_w = (long)heads * vdim + 2L * groups * n_state;
-  const int vec_bc = rows_allow_16(xbc, (long)heads * vdim, row_w, n_state) && n_state % 4 == 0;
-  const int vec_x = rows_allow_16(xbc, 0, row_w, vdim) && (GROUPS * vp) % 4 == 0 && vdim % (GROUPS * vp) == 0;
-  const dim3 grid(n_seqs, heads, (vdim + GROUPS * vp - 1) / (GROUPS * vp)), block(GROUPS * PARTS);
-#define FMS_LAUNCH(NP, VP)                                                                                              \
+  const int vec_bc = rows_allow_16(xbc, (long)heads * vdim, row_w, n_state) && n_state % 4 == 0 && shape.np % 4 == 0;
+  const int vec_x = rows_allow_16(xbc, 0, row_w, vdim) && vb % 4 == 0 && vdim % vb == 0;
+  const dim3 grid(n_seqs, heads, (vdim + vb - 1) / vb), block(SCAN_THREADS);
+#define FMS_LAUNCH(NP, VP, PARTS)                                                                                       \
   do {                                                                                                                  \
-    const size_t smem = ((size_t)2 * CH * (2 * RowLayout<NP>::ROW + GROUPS * VP) + 2 * CH) * sizeof(float);                      \
-    cudaFuncSetAttribute(selective_scan_kernel<NP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
-    fms_launch(selective_scan_kernel<NP, VP>, grid, block, smem, stream, xbc, dt_raw, dtype == FMS_BF16 ? 1 : 0, dt_stride, \
+    const size_t smem = ((size_t)2 * CH * (2 * RowLayout<NP, PARTS>::ROW + SCAN_THREADS / PARTS * VP) + 2 * CH) * sizeof(float); \
+    cudaFuncSetAttribute(selective_scan_kernel<NP, VP, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    fms_launch(selective_scan_kernel<NP, VP, PARTS>, grid, block, smem, stream, xbc, dt_raw, dtype == FMS_BF16 ? 1 : 0, dt_stride, \
                dt_bias, a_log, d_skip, state, y, first_row, slots, heads, vdim, n_state, groups, write_state, n_slots,   \
                vec_bc, vec_x);                                                                                           \
   } while (0)
@@ -630,23 +660,23 @@ FMS_API int fms_delta_rule_scan(float* qkv, const void* beta_raw, int dtype, int
                                 const int* first_row, const int* slots, int n_tokens, int n_seqs, int heads, int kvheads,
                                 int dim, int vdim, int write_state, int n_slots, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return 0;
-  if (heads <= 0 || kvheads <= 0 || heads % kvheads || dim <= 0 || dim > PARTS * 32 || vdim <= 0)
-    return fms_fail("delta_rule_scan: %d heads over %d, dim %d (up to %d), vdim %d", heads, kvheads, dim, PARTS * 32, vdim);
+  if (heads <= 0 || kvheads <= 0 || heads % kvheads || dim <= 0 || dim > 256 || vdim <= 0)
+    return fms_fail("delta_rule_scan: %d heads over %d, dim %d (up to 256), vdim %d", heads, kvheads, dim, vdim);
   FMS_DISPATCH_DTYPE(dtype, T, fms_launch(delta_prepare_kernel<T>, dim3(n_tokens, (2 * kvheads + heads + 3) / 4), dim3(128), 0, stream, qkv, (const T*)a_raw,
                                           (const T*)beta_raw, beta_stride, dt_bias, a_log, decay, beta, heads, kvheads, dim,
                                           vdim));
-  const int np = (dim + PARTS - 1) / PARTS;
-  const int vp = columns_per_thread(n_seqs, heads, vdim, np);
+  const ScanShape shape = scan_shape(n_seqs, heads, vdim, dim);
+  const int vb = SCAN_THREADS / shape.parts * shape.vp;  // value columns of a block
   const long row_w = 2L * kvheads * dim + (long)heads * vdim;
-  const int vec_qk = rows_allow_16(qkv, 0, row_w, dim) && dim % 4 == 0;
-  const int vec_g = rows_allow_16(decay, 0, (long)heads * dim, dim);
-  const int vec_v = rows_allow_16(qkv, 2L * kvheads * dim, row_w, vdim) && vdim % (GROUPS * vp) == 0 && (GROUPS * vp) % 4 == 0;
-  const dim3 grid(n_seqs, heads, (vdim + GROUPS * vp - 1) / (GROUPS * vp)), block(GROUPS * PARTS);
-#define FMS_LAUNCH(NP, VP)                                                                                              \
+  const int vec_qk = rows_allow_16(qkv, 0, row_w, dim) && shape.np % 4 == 0;
+  const int vec_g = rows_allow_16(decay, 0, (long)heads * dim, dim) && shape.np % 4 == 0;
+  const int vec_v = rows_allow_16(qkv, 2L * kvheads * dim, row_w, vdim) && vdim % vb == 0 && vb % 4 == 0;
+  const dim3 grid(n_seqs, heads, (vdim + vb - 1) / vb), block(SCAN_THREADS);
+#define FMS_LAUNCH(NP, VP, PARTS)                                                                                       \
   do {                                                                                                                  \
-    const size_t smem = ((size_t)2 * CH * (3 * RowLayout<NP>::ROW + GROUPS * VP + 1)) * sizeof(float);                           \
-    cudaFuncSetAttribute(delta_rule_scan_kernel<NP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-    fms_launch(delta_rule_scan_kernel<NP, VP>, grid, block, smem, stream, (const float*)qkv, (const float*)decay,        \
+    const size_t smem = ((size_t)2 * CH * (3 * RowLayout<NP, PARTS>::ROW + SCAN_THREADS / PARTS * VP + 1)) * sizeof(float); \
+    cudaFuncSetAttribute(delta_rule_scan_kernel<NP, VP, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    fms_launch(delta_rule_scan_kernel<NP, VP, PARTS>, grid, block, smem, stream, (const float*)qkv, (const float*)decay, \
                (const float*)beta, state, o, first_row, slots, heads, kvheads, dim, vdim, write_state, n_slots, vec_qk,  \
                vec_g, vec_v);                                                                                            \
   } while (0)

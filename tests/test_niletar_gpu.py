@@ -501,3 +501,36 @@ def test_trace_program_replays_a_batch(folders, oracles, tmp_path):
     for t in range(4):
         want = [wa[66 + t]] + ([wb[5 + t]] if t % 2 else [])
         close(read(t + 1), torch.stack(want), "fp32")
+
+
+def test_command_line_and_sampling(folders, oracles):
+    """The framework's command line finds the design through config.json: greedy tokens equal the oracle's choices; with
+    sampling (temperature, top-k) every token is among the oracle's k best given what came before."""
+    from fms_b200.utils.generation import generate
+
+    which, cfg = "p", nm.CONFIGS["p"]
+    prompts = [nm.prompt(cfg, n, 95 + i) for i, n in enumerate((4, 9))]
+    args = [sys.executable, os.path.join(ROOT, "bin", "fms_inference"), "--architecture", "hf_pretrained", "--model_path", folders[which],
+            "--default_dtype", "fp32",
+            "--batch_input", "--max_new_tokens", "6", "--deterministic"]
+    for p in prompts:
+        args += ["--prompt_ids", ",".join(str(t) for t in p)]
+    proc = subprocess.run(args, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [[int(x) for x in l.split(",")] for l in proc.stdout.splitlines() if l.strip()]
+    assert len(lines) == 2
+    for p, o in zip(prompts, lines):
+        assert o[: len(p)] == p and len(o) == len(p) + 6
+        for k in range(len(p), len(o)):
+            row = oracles[which].logits(o[:k])[-1]
+            best = row.topk(2).values
+            if best[0] - best[1] > 1e-3:
+                assert o[k] == int(row.argmax())
+    out = generate(model_of(folders, which, "fp32"), [torch.tensor(p) for p in prompts], max_new_tokens=8, do_sample=True,
+                   temperature=0.8, top_k=3, seed=5)
+    for p, o in zip(prompts, out):
+        o = o.tolist()
+        for k in range(len(p), len(o)):
+            row = oracles[which].logits(o[:k])[-1]
+            kth = row.topk(4).values
+            assert row[o[k]] >= kth[2] - 1e-4 or kth[2] - kth[3] < 1e-3
