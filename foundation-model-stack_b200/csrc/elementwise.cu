@@ -728,18 +728,46 @@ FMS_API int fms_scaled_add_rmsnorm(float* residual, float alpha, const void* da,
   return fms_launch_status("scaled_add_rmsnorm");
 }
 
+// four consecutive values at once (the pointer aligned to four values)
+__device__ __forceinline__ void ldv4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void ldv4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+  v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+__device__ __forceinline__ void stv4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void stv4(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<const uint32_t*>(&a);
+  t.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
 // float32 rows in the compute dtype (the stream as a sublayer's input where nothing else has made that copy)
 template <typename T>
 __global__ void cast_rows_kernel(const float* x, T* out, size_t n) {
   pdl_launch_dependents();
   pdl_wait();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) out[i] = from_f32<T>(x[i]);
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i + 4 <= n) {
+    float v[4];
+    ldv4(x + i, v);
+    stv4(out + i, v);
+  } else {
+    for (size_t k = i; k < n; ++k) out[k] = from_f32<T>(x[k]);
+  }
 }
 
 FMS_API int fms_cast_rows(const float* x, void* out, int dtype, long n, cudaStream_t stream) {
   if (n <= 0) return 0;
-  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(cast_rows_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x,
+  if ((uintptr_t)x % 16 || (uintptr_t)out % 16) return fms_fail("cast_rows: rows that do not start on 16 bytes");
+  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(cast_rows_kernel<T>, dim3((unsigned)((n + 1023) / 1024)), dim3(256), 0, stream, x,
                                           (T*)out, (size_t)n));
   return fms_launch_status("cast_rows");
 }
@@ -854,26 +882,45 @@ FMS_API int fms_qk_prepare_store(const void* proj, int dtype, int stride, void* 
 // gate on the heads' results: out[t, h * vdim + e] = factor * o[t, h * pad + e] * sigmoid(gate[t, h * vdim + e]),
 // e < vdim; o has rows of nheads * pad, gate is a run of columns of a wider matrix (row stride gate_stride)
 // ---------------------------------------------------------------------------------------------------
-template <typename T>
+// VEC values a thread (4 where the sizes and addresses allow accesses of 4 values, else 1)
+template <typename T, int VEC>
 __global__ void sigmoid_gate_kernel(const T* o, const T* gate, int gate_stride, T* out, int nheads, int vdim, int pad,
                                     float factor, size_t total) {
   pdl_launch_dependents();
   pdl_wait();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (i >= total) return;
   const int width = nheads * vdim;
   const size_t t = i / width;
   const int c = (int)(i - t * width), h = c / vdim, e = c - h * vdim;
-  float v = to_f32(o[(t * nheads + h) * pad + e]) * factor;
-  if (gate) v *= 1.f / (1.f + expf(-to_f32(gate[t * gate_stride + c])));
-  out[i] = from_f32<T>(v);
+  if constexpr (VEC == 4) {
+    float v[4], g[4];
+    ldv4(o + (t * nheads + h) * pad + e, v);
+    if (gate) ldv4(gate + t * gate_stride + c, g);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = v[k] * factor * (gate ? 1.f / (1.f + expf(-g[k])) : 1.f);
+    stv4(out + i, v);
+  } else {
+    float v = to_f32(o[(t * nheads + h) * pad + e]) * factor;
+    if (gate) v *= 1.f / (1.f + expf(-to_f32(gate[t * gate_stride + c])));
+    out[i] = from_f32<T>(v);
+  }
 }
 
 FMS_API int fms_sigmoid_gate(const void* o, const void* gate, int gate_stride, void* out, int dtype, int n_tokens,
                              int nheads, int vdim, int pad, float factor, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const size_t total = (size_t)n_tokens * nheads * vdim;
-  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(sigmoid_gate_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
-                                          (const T*)o, (const T*)gate, gate_stride, (T*)out, nheads, vdim, pad, factor, total));
+  const size_t item = dtype == FMS_BF16 ? 2 : 4;
+  const bool four = vdim % 4 == 0 && pad % 4 == 0 && (uintptr_t)o % (4 * item) == 0 && (uintptr_t)out % (4 * item) == 0 &&
+                    (gate == nullptr || (gate_stride % 4 == 0 && (uintptr_t)gate % (4 * item) == 0));
+  if (four) {
+    FMS_DISPATCH_DTYPE(dtype, T, fms_launch(sigmoid_gate_kernel<T, 4>, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0,
+                                            stream, (const T*)o, (const T*)gate, gate_stride, (T*)out, nheads, vdim, pad,
+                                            factor, total));
+  } else {
+    FMS_DISPATCH_DTYPE(dtype, T, fms_launch(sigmoid_gate_kernel<T, 1>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                                            (const T*)o, (const T*)gate, gate_stride, (T*)out, nheads, vdim, pad, factor, total));
+  }
   return fms_launch_status("sigmoid_gate");
 }

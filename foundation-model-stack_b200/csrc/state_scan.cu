@@ -504,8 +504,30 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_rule_scan_kernel(const flo
 // x [tokens, width] float32; groups of `gs` values; weight[c % weight_period]; gate: columns of rows of gate_stride
 // values.  gate_mode 1: x * silu(gate) before the norm;  2: sigmoid(gate) after the norm and the weight;  0: none.
 // One warp per (token, group).
-// TPU threads per (token, group): a warp, or a block of 256 where the groups are long
-template <typename T, int TPU>
+// four consecutive values at once (the pointer aligned to four values)
+__device__ __forceinline__ void ld4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void ld4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+  v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+__device__ __forceinline__ void st4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<const uint32_t*>(&a);
+  t.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+// TPU threads per (token, group): a warp, or a block of 256 where the groups are long; VEC values a thread at a time
+// (4 where the sizes and addresses allow it)
+template <typename T, int TPU, int VEC>
 __global__ void gated_group_rmsnorm_kernel(const float* x, const T* gate, int gate_stride, int gate_mode,
                                            const float* weight, int weight_period, float eps, float factor, T* out,
                                            int n_tokens, int width, int gs) {
@@ -521,27 +543,43 @@ __global__ void gated_group_rmsnorm_kernel(const float* x, const T* gate, int ga
   const float* xr = x + t * width + c0;
   const T* gr = gate ? gate + t * gate_stride + c0 : nullptr;
   float ss = 0.f;
-  for (int e = lane; e < gs; e += TPU) {
-    float v = xr[e];
-    if (gate_mode == 1) {
-      const float z = to_f32(gr[e]);
-      v *= z * sigmoid_f(z);
+  for (int e = lane * VEC; e < gs; e += TPU * VEC) {
+    float v[VEC], z[VEC];
+    if constexpr (VEC == 4) {
+      ld4(xr + e, v);
+      if (gate_mode == 1) ld4(gr + e, z);
+    } else {
+      v[0] = xr[e];
+      if (gate_mode == 1) z[0] = to_f32(gr[e]);
     }
-    ss = fmaf(v, v, ss);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      if (gate_mode == 1) v[k] *= z[k] * sigmoid_f(z[k]);
+      ss = fmaf(v[k], v[k], ss);
+    }
   }
   float total;
   if constexpr (TPU == 32) total = warp_sum(ss);
   else total = block_sum(ss, scratch);
   const float inv = 1.f / sqrtf(total / (float)gs + eps);
-  for (int e = lane; e < gs; e += TPU) {
-    float v = xr[e];
-    if (gate_mode == 1) {
-      const float z = to_f32(gr[e]);
-      v *= z * sigmoid_f(z);
+  for (int e = lane * VEC; e < gs; e += TPU * VEC) {
+    float v[VEC], z[VEC];
+    if constexpr (VEC == 4) {
+      ld4(xr + e, v);
+      if (gate_mode != 0) ld4(gr + e, z);
+    } else {
+      v[0] = xr[e];
+      if (gate_mode != 0) z[0] = to_f32(gr[e]);
     }
-    v = v * inv * weight[(c0 + e) % weight_period];
-    if (gate_mode == 2) v *= sigmoid_f(to_f32(gr[e]));
-    out[t * width + c0 + e] = from_f32<T>(v * factor);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      if (gate_mode == 1) v[k] *= z[k] * sigmoid_f(z[k]);
+      v[k] = v[k] * inv * weight[(c0 + e + k) % weight_period];
+      if (gate_mode == 2) v[k] *= sigmoid_f(z[k]);
+      v[k] *= factor;
+    }
+    if constexpr (VEC == 4) st4(out + t * width + c0 + e, v);
+    else out[t * width + c0 + e] = from_f32<T>(v[0]);
   }
 }
 }  // namespace
@@ -693,14 +731,20 @@ FMS_API int fms_gated_group_rmsnorm(const float* x, const void* gate, int dtype,
     return fms_fail("gated_group_rmsnorm: rows of %d in groups of %d", width, group_size);
   if (gate_mode != 0 && gate == nullptr) return fms_fail("gated_group_rmsnorm: a gate mode without a gate");
   const size_t units = (size_t)n_tokens * (width / group_size);
+  const size_t item = dtype == FMS_BF16 ? 2 : 4;
+  const bool four = group_size % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % (4 * item) == 0 &&
+                    (gate == nullptr || (gate_stride % 4 == 0 && (uintptr_t)gate % (4 * item) == 0));
+#define FMS_NORM(TPU, VEC, BLOCKS, THREADS)                                                                              \
+  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(gated_group_rmsnorm_kernel<T, TPU, VEC>, dim3((unsigned)(BLOCKS)), dim3(THREADS), 0,  \
+                                          stream, x, (const T*)gate, gate_stride, gate_mode, weight, weight_period, eps, \
+                                          factor, (T*)out, n_tokens, width, group_size))
   if (group_size >= 512) {
-    FMS_DISPATCH_DTYPE(dtype, T, fms_launch(gated_group_rmsnorm_kernel<T, 256>, dim3((unsigned)units), dim3(256), 0, stream, x,
-                                            (const T*)gate, gate_stride, gate_mode, weight, weight_period, eps, factor,
-                                            (T*)out, n_tokens, width, group_size));
+    if (four) FMS_NORM(256, 4, units, 256);
+    else FMS_NORM(256, 1, units, 256);
   } else {
-    FMS_DISPATCH_DTYPE(dtype, T, fms_launch(gated_group_rmsnorm_kernel<T, 32>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0,
-                                            stream, x, (const T*)gate, gate_stride, gate_mode, weight, weight_period, eps,
-                                            factor, (T*)out, n_tokens, width, group_size));
+    if (four) FMS_NORM(32, 4, (units + 3) / 4, 128);
+    else FMS_NORM(32, 1, (units + 3) / 4, 128);
   }
+#undef FMS_NORM
   return fms_launch_status("gated_group_rmsnorm");
 }
