@@ -503,6 +503,23 @@ def test_trace_program_replays_a_batch(folders, oracles, tmp_path):
         close(read(t + 1), torch.stack(want), "fp32")
 
 
+def test_trace_program_with_many_short_requests_and_no_room_to_spare(folders, oracles, tmp_path):
+    """Six requests of three tokens in one batch with --max-tokens 18, the tokens they hold and not one more: the
+    cache's blocks of 64 tokens must not make the program run out of room."""
+    which, cfg = "q", nm.CONFIGS["q"]
+    reqs = [nm.prompt(cfg, 3, 120 + i) for i in range(6)]
+    steps = [{"step": 0, "entries": [{"id": str(i), "tokens": r[:2], "want": [1]} for i, r in enumerate(reqs)], "end": []},
+             {"step": 1, "entries": [{"id": str(i), "tokens": r[2:], "want": [0]} for i, r in enumerate(reqs)],
+              "end": [str(i) for i in range(6)]}]
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders[which], "--dtype",
+                           "float32", "--out", str(tmp_path), "--max-tokens", "18"],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    read = lambda i: torch.from_numpy(np.fromfile(os.path.join(str(tmp_path), f"{i}.f32"), dtype="<f4").reshape(-1, cfg["vocab"]))
+    close(read(0), torch.stack([oracles[which].logits(r)[1] for r in reqs]), "fp32")
+    close(read(1), torch.stack([oracles[which].logits(r)[2] for r in reqs]), "fp32")
+
+
 def test_command_line_and_sampling(folders, oracles):
     """The framework's command line finds the design through config.json: greedy tokens equal the oracle's choices; with
     sampling (temperature, top-k) every token is among the oracle's k best given what came before."""
