@@ -26,7 +26,7 @@ constexpr int CH = 16;      // tokens brought into shared memory at a time
 constexpr int MAX_TAPS = 16;
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
-__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+__device__ __forceinline__ double softplus_d(double v) { return v > 40.0 ? v : log1p(exp(v)); }
 
 // ---- causal convolution ------------------------------------------------------------------------------
 // x: rows of `stride` values (the convolved channels are its first `channels` from the pointer on); a block per
@@ -288,7 +288,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const floa
   const int cols = min(VB, vdim - v0);  // value columns this block really has
   if (n_state != PARTS * NP || cols != VB)
     for (int i = tid; i < 2 * STAGE; i += blockDim.x) smem[i] = 0.f;  // the padding stays zero from here on
-  const float A = expf(a_log[head]), D = d_skip[head], bias = dt_bias[head];
+  const double A = exp((double)a_log[head]);
+  const float D = d_skip[head], bias = dt_bias[head];
   float s[VP][NP];
 #pragma unroll
   for (int i = 0; i < VP; ++i) {
@@ -314,9 +315,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const floa
     if (tid < cn) {
       const size_t at = (size_t)(c0 + tid) * dt_stride + head;
       const float raw = dt_is_bf16 ? __bfloat162float(((const __nv_bfloat16*)dt_raw)[at]) : ((const float*)dt_raw)[at];
-      const float dt = softplus_f(raw + bias);
-      sdt[tid] = dt;
-      sdec[tid] = expf(-A * dt);
+      // A decay is applied once a token and its error compounds over a sequence: the step size and the decay are taken
+      // in double and rounded once (expf alone may be two units off in the last place)
+      const double dt = softplus_d((double)raw + (double)bias);
+      sdt[tid] = (float)dt;
+      sdec[tid] = (float)exp(-A * dt);
     }
     if (more) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
@@ -387,10 +390,10 @@ __global__ void delta_prepare_kernel(float* qkv, const T* a_raw, const T* beta_r
       for (int n = lane; n < dim; n += 32) x[n] *= inv;
     } else {
       const int h = item - 2 * kvheads;
-      const float A = expf(a_log[h]);
+      const double A = exp((double)a_log[h]);  // decays compound over a sequence: taken in double, rounded once
       const size_t at = ((size_t)t * heads + h) * dim;
       for (int n = lane; n < dim; n += 32)
-        decay[at + n] = expf(-A * softplus_f(to_f32(a_raw[at + n]) + dt_bias[(size_t)h * dim + n]));
+        decay[at + n] = (float)exp(-A * softplus_d((double)to_f32(a_raw[at + n]) + (double)dt_bias[(size_t)h * dim + n]));
       if (lane == 0) beta[(size_t)t * heads + h] = sigmoid_f(to_f32(beta_raw[(size_t)t * beta_stride + h]));
     }
   }
