@@ -69,7 +69,7 @@ CONFIGS = {
                 eps=1e-6),
     # heads of 128 keys and 64 values (the tensor-core attention kernels in bfloat16), a delta rule with 96 key channels
     # and 40 values (two runs of value columns), a state of 128 rows
-    "s": config(101, 64, 3.0, [_S_PAR, mamba2(2, 48, 128, 2, 2, 4, dense(72)), dict(_S_PAR, weights_of=0)]),
+    "s": config(101, 64, 1.5, [_S_PAR, mamba2(2, 48, 128, 2, 2, 4, dense(72)), dict(_S_PAR, weights_of=0)]),
 }
 RANKS = {"p": (5, 3), "q": (8, 16), "r": (3, 7), "s": (16, 8)}  # of the decay's and the gate's low-rank pairs
 
