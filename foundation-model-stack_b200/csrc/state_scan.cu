@@ -1,5 +1,6 @@
 // Mixers that carry a matrix of state per head from token to token, and the short causal convolutions in front of
-// them.  Everything that enters a recurrence is float32: step sizes, decays, gates, unit norms, the state itself;
+// them.  Everything that enters a recurrence is float32: step sizes, decays, gates, unit norms, the state itself
+// (step sizes and decays are taken in double and rounded to float32 once: a decay's error compounds over a sequence);
 // the state of every sequence lies in float32 between steps and a step starts from what its slot holds.
 //
 //   causal_conv         y[t, c] = act(bias[c] + sum_j w[c, j] x[t - (taps - 1) + j, c]) over the rows of one sequence;
@@ -8,15 +9,16 @@
 //   selective_scan      per head, S [state, vdim]:  S = exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x
 //                       with dt = softplus(dt_raw + dt_bias); B and C are shared by the heads of a group
 //   delta_rule_scan     per head, S [dim, vdim]:  S = diag(g) S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q
-//                       with q, k unit vectors (q also times dim^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias))
+//                       with q, k unit vectors (q also times dim^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)),
+//                       all of which delta_prepare makes ready for every token before the scan starts
 //   gated_group_rmsnorm rows cut into groups, each divided by its own root mean square, times a weight; a gate
 //                       multiplies either before the norm (silu) or after it (sigmoid)
 //
-// The scans walk a sequence's tokens in order: one thread block per (sequence, head, run of value columns), a thread
-// per (value column, every fourth state row) with its part of the state in registers; the tokens' vectors come
-// through shared memory sixteen tokens at a time, and the four threads of a column add their sums by shuffles.  The
-// order of the sums does not depend on how a prompt was cut into steps or on what else is in the batch.
-// State layout: [slots, heads, vdim, rows] (the state's rows contiguous), so that a thread's part is one run.
+// The scans walk a sequence's tokens in order: one thread block per (sequence, head, run of value columns); a thread
+// holds a run of state rows of one, two or four value columns in registers; the tokens' vectors come through shared
+// memory sixteen tokens at a time (cp.async, two stages), and the 8, 16 or 32 threads that share a column add their
+// sums by shuffles.  The order of the sums does not depend on how a prompt was cut into steps or on what else is in
+// the batch.  State layout: [slots, heads, vdim, rows] (the state's rows contiguous), so that a thread's part is one run.
 #include "common.cuh"
 
 // Kernels of a step may start while the kernel before them still runs (programmatic dependent launch); no pointer
@@ -632,8 +634,13 @@ static ScanShape scan_shape(int n_seqs, int heads, int vdim, int rows) {
   s.np = need <= 2 ? 2 : (need <= 4 ? 4 : (need <= 8 ? 8 : (need <= 16 ? 16 : 32)));
   const int groups = SCAN_THREADS / s.parts;
   s.vp = 1;
+  static int min_blocks = -1;  // FMS_B200_SCAN_BLOCKS: blocks that must remain for a thread to take more columns (592)
+  if (min_blocks < 0) {
+    const char* e = getenv("FMS_B200_SCAN_BLOCKS");
+    min_blocks = e ? atoi(e) : 592;
+  }
   for (int vp = s.np >= 32 ? 2 : 4; vp > 1; vp >>= 1)
-    if ((long)n_seqs * heads * ((vdim + groups * vp - 1) / (groups * vp)) >= 592 && vdim >= groups * vp) {
+    if ((long)n_seqs * heads * ((vdim + groups * vp - 1) / (groups * vp)) >= min_blocks && vdim >= groups * vp) {
       s.vp = vp;
       break;
     }
