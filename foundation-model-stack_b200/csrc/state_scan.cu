@@ -627,9 +627,14 @@ struct ScanShape {
 };
 static ScanShape scan_shape(int n_seqs, int heads, int vdim, int rows) {
   ScanShape s;
+  static int few = -1;  // FMS_B200_SCAN_FEW: blocks of a single sequence below which more threads share a column group
+  if (few < 0) {
+    const char* e = getenv("FMS_B200_SCAN_FEW");
+    few = e ? atoi(e) : 148;
+  }
   s.parts = 8;
-  if ((long)heads * ((vdim + 15) / 16) < 148 && rows >= 64) s.parts = 16;
-  if (s.parts == 16 && (long)heads * ((vdim + 7) / 8) < 148 && rows >= 128) s.parts = 32;
+  if ((long)heads * ((vdim + 15) / 16) < few && rows >= 64) s.parts = 16;
+  if (s.parts == 16 && (long)heads * ((vdim + 7) / 8) < few && rows >= 128) s.parts = 32;
   const int need = (rows + s.parts - 1) / s.parts;
   s.np = need <= 2 ? 2 : (need <= 4 ? 4 : (need <= 8 ? 8 : (need <= 16 ? 16 : 32)));
   const int groups = SCAN_THREADS / s.parts;
