@@ -69,7 +69,10 @@ class Model:
         from ..cache.requests import KVRequest
 
         itemsize = 4 if self.dtype == torch.float32 else 2
-        return sum(r.planes * r.kvheads * r.head_dim * itemsize for r in self.decoder.cache_requests() if isinstance(r, KVRequest))
+        flat = []
+        for r in self.decoder.cache_requests():  # a mixer that keeps several things asks with a tuple
+            flat += list(r) if isinstance(r, (tuple, list)) else [r]
+        return sum(r.planes * r.kvheads * r.head_dim * itemsize for r in flat if isinstance(r, KVRequest))
 
     def engine(self, min_tokens: int = 0, min_slots: int = 0):
         """The model's own engine, made on first use and made anew when it is too small."""

@@ -44,6 +44,7 @@ def test_config_json_round_trip_registry_and_shared_layers(tmp_path):
     assert isinstance(kv, KVRequest) and kv.head_dim == 32 and kv.kvheads == 1  # heads of 24 and 8, padded to 32
     assert isinstance(matrix, StateRequest) and matrix.shape == (4, 20, 12) and tail.shape == (1, 2 * 12 + 2 * 12 + 4 * 20)
     assert requests[0][0].shape == (3, 8, 5) and requests[0][1].shape == (2, 3 * 8 + 2 * 5)
+    assert model.cache_bytes_per_token() == 2 * (2 * 1 * 32 * 4)  # two attention layers, keys and values, float32
     out = json.loads(json.dumps(model.config_json()))
     for layer in out["layers"]:  # what the loader read from the shapes is the only thing added
         if layer["type"] == "parallel":
